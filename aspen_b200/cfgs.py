@@ -1,0 +1,187 @@
+"""Darknet-style .cfg text for the benchmark networks, generated from their architecture.
+
+The ASPEN cfg dialect is the one `parse_section` reads (reference src/darknet_parser.c:455-552):
+`[net]`, `[convolutional]`, `[maxpool]`, `[avgpool]`, `[shortcut]`, `[connected]`, `[matmul]`,
+`[attention_k]`, `[attention_v]`, `[layernorm]` with keys size/stride/pad/filters/output/parent/from/
+M/K/n_head/n_embd/masked/activation.  Each builder returns `(cfg_text, weighted_layers)` where
+`weighted_layers` lists, in file order, the layers that own weights -- the order the `LAYER:n`
+counter of the weight file follows (reference src/apu_file_io.c:85-100).
+
+Every entry of `weighted_layers` is `(kind, weight_shape, fan_in)`; weight_shape is the on-disk
+shape: conv OIHW, connected [O][C][H][W], matmul [M][K], layernorm [M].
+"""
+from __future__ import annotations
+
+
+class _Cfg:
+    def __init__(self):
+        self.lines: list[str] = []
+        self.weighted: list[tuple[str, tuple[int, ...], int]] = []
+
+    def sec(self, name: str, **kv):
+        self.lines.append(f"[{name}]")
+        for k, v in kv.items():
+            if v is not None:
+                self.lines.append(f"{k}={v}")
+        self.lines.append("")
+
+    def text(self) -> str:
+        return "\n".join(self.lines) + "\n"
+
+
+def _conv(c: _Cfg, cin: int, cout: int, size: int, stride: int, pad: int, act: str, parent=None, bn=True):
+    c.sec("convolutional", parent=parent, batch_normalize=1 if bn else None, filters=cout, size=size,
+          stride=stride, pad=pad, activation=act)
+    c.weighted.append(("conv", (cout, cin, size, size), cin * size * size))
+    return cout
+
+
+def resnet50():
+    """ResNet-50 v1.5 (stride on the 3x3), BN folded, 1000-way classifier as a 1x1 conv:
+    73 sections like the reference's files/resnet50/resnet50_aspen.cfg."""
+    c = _Cfg()
+    c.sec("net", height=224, width=224, channels=3)
+    ch = _conv(c, 3, 64, 7, 2, 3, "relu")
+    c.sec("maxpool", size=3, stride=2, pad=1)
+    for width, blocks, stride in ((64, 3, 1), (128, 4, 2), (256, 6, 2), (512, 3, 2)):
+        for b in range(blocks):
+            cin = ch
+            s = stride if b == 0 else 1
+            _conv(c, cin, width, 1, 1, 0, "relu")
+            _conv(c, width, width, 3, s, 1, "relu")
+            ch = _conv(c, width, width * 4, 1, 1, 0, "linear")
+            if b == 0:
+                _conv(c, cin, width * 4, 1, s, 0, "linear", parent=-4)
+                c.sec("shortcut", **{"from": -2}, activation="relu")
+            else:
+                c.sec("shortcut", **{"from": -4}, activation="relu")
+    c.sec("avgpool", size=7, stride=1)
+    _conv(c, ch, 1000, 1, 1, 0, "linear", bn=False)
+    return c.text(), c.weighted
+
+
+def vgg16():
+    """VGG-16: conv blocks [2,2,3,3,3] x (64,128,256,512,512), 2x2 maxpools, FC 25088-4096-4096-1000."""
+    c = _Cfg()
+    c.sec("net", height=224, width=224, channels=3)
+    ch, hw = 3, 224
+    for n, width in ((2, 64), (2, 128), (3, 256), (3, 512), (3, 512)):
+        for _ in range(n):
+            ch = _conv(c, ch, width, 3, 1, 1, "relu", bn=False)
+        c.sec("maxpool", size=2, stride=2)
+        hw //= 2
+    feat = (ch, hw, hw)
+    for out, act in ((4096, "relu"), (4096, "relu"), (1000, "linear")):
+        c.sec("connected", output=out, activation=act)
+        c.weighted.append(("fc", (out,) + feat, feat[0] * feat[1] * feat[2]))
+        feat = (out, 1, 1)
+    return c.text(), c.weighted
+
+
+def custom_cifar():
+    """The small CIFAR-10 net of the reference's third example (files/custom.cfg)."""
+    c = _Cfg()
+    c.sec("net", height=32, width=32, channels=3)
+    _conv(c, 3, 32, 5, 1, 2, "relu", bn=False)
+    c.sec("maxpool", size=2, stride=2)
+    _conv(c, 32, 64, 3, 1, 1, "relu", bn=False)
+    c.sec("maxpool", size=2, stride=2)
+    feat = (64, 8, 8)
+    for out, act in ((256, "relu"), (128, "relu"), (10, "linear")):
+        c.sec("connected", output=out, activation=act)
+        c.weighted.append(("fc", (out,) + feat, feat[0] * feat[1] * feat[2]))
+        feat = (out, 1, 1)
+    return c.text(), c.weighted
+
+
+def _matmul(c: _Cfg, m: int, k: int, parent=None, heads=None, embd=None, act=None):
+    c.sec("matmul", parent=parent, M=m, n_head=heads, n_embd=embd, activation=act)
+    c.weighted.append(("matmul", (m, k), k))
+
+
+def _layernorm(c: _Cfg, m: int):
+    c.sec("layernorm", M=m)
+    c.weighted.append(("layernorm", (m,), m))
+
+
+def transformer(layers: int, d: int, heads: int, ffn: int, pre_ln: bool, masked: bool, act: str,
+                final_ln: bool = False, lm_head: int = 0):
+    """Encoder/decoder stack in the reference's layer vocabulary.  post-LN + `gelu` is
+    files/bert_base/bert_base_aspen.cfg; pre-LN + `masked=1` + `gelu_acc` is
+    files/gpt2_124M/gpt2_124M_aspen.cfg.  `final_ln`/`lm_head` append the GPT-2 tail the
+    reference cfg leaves out (same layer types, nothing new for the runtime)."""
+    c = _Cfg()
+    c.sec("net", M=d, height=1, filters=d)
+    hd = d // heads
+    for _ in range(layers):
+        if pre_ln:
+            _layernorm(c, d)
+        _matmul(c, d, d, heads=heads, embd=d)                 # keys   (PARENT_1 of attention_k)
+        _matmul(c, d, d, parent=-2, heads=heads, embd=d)      # queries (PARENT_0 of attention_k)
+        _matmul(c, d, d, parent=-3, heads=heads, embd=d)      # values
+        c.sec("attention_k", parent=-2, **{"from": -3}, M=1, K=hd, n_head=heads, n_embd=d,
+              masked=1 if masked else None)
+        c.sec("attention_v", **{"from": -2}, M=d, n_head=heads, n_embd=d)
+        _matmul(c, d, d)
+        c.sec("shortcut", **{"from": -8 if pre_ln else -7}, M=d)
+        _layernorm(c, d)
+        _matmul(c, ffn, d, act=act)
+        _matmul(c, d, ffn)
+        c.sec("shortcut", **{"from": -4 if pre_ln else -3}, M=d)
+        if not pre_ln:
+            _layernorm(c, d)
+    if final_ln:
+        _layernorm(c, d)
+    if lm_head:
+        _matmul(c, lm_head, d)
+    return c.text(), c.weighted
+
+
+def bert_base():
+    return transformer(12, 768, 12, 3072, pre_ln=False, masked=False, act="gelu")
+
+
+def gpt2_124m(with_lm_head: bool = False):
+    return transformer(12, 768, 12, 3072, pre_ln=True, masked=True, act="gelu_acc",
+                       final_ln=with_lm_head, lm_head=50257 if with_lm_head else 0)
+
+
+def tiny_cnn():
+    """A few-layer CNN that touches conv 3x3/1x1/strided, both pools, residual and connected;
+    small enough for pure-CPU checks."""
+    c = _Cfg()
+    c.sec("net", height=20, width=20, channels=3)
+    _conv(c, 3, 16, 3, 1, 1, "relu", bn=False)
+    c.sec("maxpool", size=3, stride=2, pad=1)
+    _conv(c, 16, 24, 1, 1, 0, "leaky", bn=False)
+    _conv(c, 24, 24, 3, 1, 1, "relu", bn=False)
+    _conv(c, 24, 24, 1, 1, 0, "linear", bn=False)
+    c.sec("shortcut", **{"from": -3}, activation="relu")
+    _conv(c, 24, 64, 3, 2, 1, "relu", bn=False)   # 64 rows: a connected layer needs an unpadded parent
+    c.sec("avgpool", size=5, stride=1)
+    c.sec("connected", output=10, activation="linear")
+    c.weighted.append(("fc", (10, 64, 1, 1), 64))
+    c.sec("softmax", output=10)
+    return c.text(), c.weighted
+
+
+def tiny_transformer(masked: bool = False, pre_ln: bool = False):
+    return transformer(2, 64, 4, 128, pre_ln=pre_ln, masked=masked, act="gelu_acc" if masked else "gelu")
+
+
+BUILDERS = {
+    "resnet50": resnet50,
+    "vgg16": vgg16,
+    "custom": custom_cifar,
+    "bert_base": bert_base,
+    "gpt2_124M": gpt2_124m,
+    "tiny_cnn": tiny_cnn,
+    "tiny_transformer": tiny_transformer,
+}
+
+
+def write_cfg(name: str, path: str, **kw):
+    text, weighted = BUILDERS[name](**kw)
+    with open(path, "w") as f:
+        f.write(text)
+    return weighted

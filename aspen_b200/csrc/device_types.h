@@ -1,0 +1,73 @@
+// Flattened device image of a tile graph (nasm) and the scheduler's control block.
+// Shared by the host uploader (engine.cu) and the kernels.
+#pragma once
+#include <cstdint>
+
+// Layer types / activations use the ABI enum values of include/aspen_b200.h.
+
+struct LayerDev {
+    int type;                 // LAYER_TYPE
+    int act;                  // LAYER_ACT
+    float *out;               // own activation matrix: column-major, H rows contiguous, W columns
+    unsigned ldc, H, W;       // column stride (floats), logical rows, columns
+    const float *in0;         // PARENT_0 activations
+    unsigned ld0, H0;
+    const float *in1;         // PARENT_1 activations
+    unsigned ld1, H1;
+    const float *weight;      // [rows][Kpad] fp32, K contiguous, zero padded; layernorm: gain[rows]
+    const float *bias;        // [rows]
+    unsigned K, Kpad, rows;
+    unsigned IC, IH, IW, OH, OW, KH, KW, stride, pad;     // conv / pool geometry
+    unsigned seq, heads, hd, masked;                     // attention
+    unsigned p_out_c, p_in_c, p_stride;                  // yolo / append raw cfg parameters
+    const float *anchors;
+    int wmap;                 // index of the weight tensor map, -1 if none
+    unsigned a_vec4;          // activation rows can be fetched in 16-byte pieces (IC % 4 == 0 ...)
+};
+
+struct TileDev {
+    unsigned layer;
+    unsigned pos_h, pos_w;    // position in the layer's output matrix
+    unsigned tile_h, tile_w;  // clipped extents
+    unsigned child_off, child_cnt;
+    unsigned need;            // number of parent tiles (true dependencies)
+};
+
+struct NasmDev {
+    const LayerDev *layers;
+    const TileDev *tiles;
+    const unsigned *children;        // CSR payload: local tile ids
+    unsigned *dep;                   // [n_tiles] parents completed so far
+    const unsigned *dep_init;        // [n_tiles] parents that are input tiles (complete when armed)
+    unsigned *layer_done;            // [n_layers] tiles completed per layer
+    const unsigned *layer_tiles;     // [n_layers]
+    const unsigned *init_ready;      // local ids of tiles runnable right after arming
+    unsigned *layers_completed;      // single counter
+    volatile unsigned *completed;    // mapped host flag, set when every layer is complete
+    const void *wmaps;               // CUtensorMap[]
+    unsigned n_tiles, n_layers, n_init, n_input_tiles;
+    unsigned tile_base;              // global id of local tile 0 in this run
+    unsigned queue_base;             // where this graph's initial ready tiles go in the queue
+};
+
+struct CtrlDev {
+    unsigned head;           // next ticket to hand out
+    unsigned tail;           // next free queue slot
+    unsigned done;           // tiles completed (input tiles included)
+    unsigned total;          // tiles in this run
+    unsigned cap;            // queue capacity (== total)
+    unsigned abort;          // set with a status code: everybody leaves
+    unsigned stop;           // host request: leave after the current tile
+    unsigned n_nasm;
+    unsigned long long stall_ns;   // no-progress window after which a wait gives up
+    unsigned pipe_spins;           // spin budget of in-kernel pipeline waits
+    unsigned pad_;
+};
+
+struct StatusHost {          // mapped host memory
+    volatile unsigned status;        // ASPEN_B200_ERR_*
+    volatile unsigned info0, info1;  // where it gave up (tile id / barrier id)
+    volatile unsigned tiles_done;
+};
+
+#define ASPEN_TILE_NONE 0xffffffffu

@@ -1,0 +1,654 @@
+// Host side of the device engine: uploads weights and flattened tile graphs, owns the stream,
+// launches the persistent scheduler, and moves inputs / results.  The only translation unit of
+// the library that calls the CUDA runtime.  There is no CPU execution path: without a usable
+// sm_100 device every entry point fails with an error.
+#include "internal.h"
+#include "scheduler.cuh"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <algorithm>
+#include <mutex>
+#include <sched.h>
+#include <unordered_map>
+
+#define CUDA_TRY(expr)                                                                          \
+    do {                                                                                        \
+        cudaError_t err__ = (expr);                                                             \
+        if (err__ != cudaSuccess) {                                                             \
+            ASPEN_ERR("CUDA error %s at %s: %s\n", cudaGetErrorName(err__), #expr, cudaGetErrorString(err__)); \
+            return -1;                                                                          \
+        }                                                                                       \
+    } while (0)
+
+static thread_local int g_device = -1;
+
+extern "C" int aspen_b200_set_device(int device) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) {
+        ASPEN_ERR("aspen_b200_set_device: device %d not available (%d visible)\n", device, n);
+        return -1;
+    }
+    g_device = device;
+    return cudaSetDevice(device) == cudaSuccess ? 0 : -1;
+}
+
+int engine_current_device() {
+    if (g_device >= 0) return g_device;
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess) return 0;
+    return d;
+}
+
+// ---- device copies of a dnn's weights ----------------------------------------------------------
+struct DeviceDnn {
+    int device = 0;
+    // per layer, per precision mode (0: rounded to TF32, 1: exact fp32)
+    std::vector<float *> weight[2];
+    std::vector<float *> bias;
+    std::vector<float *> anchors;
+    std::vector<unsigned> kpad;
+    bool have[2] = {false, false};
+};
+
+static float round_to_tf32(float x) {
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    if ((u & 0x7f800000u) == 0x7f800000u) return x;
+    u += 0x00001000u;          // round to nearest, ties away: 13 mantissa bits are dropped
+    u &= 0xffffe000u;
+    memcpy(&x, &u, 4);
+    return x;
+}
+
+static int upload_weights(aspen_dnn_t *dnn, int device, int precision, DeviceDnn **out) {
+    if (device < 0 || device >= 16) { ASPEN_ERR("device index %d out of range\n", device); return -1; }
+    DeviceDnn *dd = dnn->dev[device];
+    if (!dd) {
+        dd = new DeviceDnn();
+        dd->device = device;
+        dd->weight[0].assign(dnn->num_layers, nullptr);
+        dd->weight[1].assign(dnn->num_layers, nullptr);
+        dd->bias.assign(dnn->num_layers, nullptr);
+        dd->anchors.assign(dnn->num_layers, nullptr);
+        dd->kpad.assign(dnn->num_layers, 0);
+        dnn->dev[device] = dd;
+    }
+    *out = dd;
+    if (dd->have[precision]) return 0;
+    for (unsigned i = 0; i < dnn->num_layers; i++) {
+        aspen_layer_t &l = dnn->layers[i];
+        aspen_tensor_t *w = l.tensors[WEIGHT_TENSOR], *b = l.tensors[BIAS_TENSOR], *a = l.tensors[ANCHOR_TENSOR];
+        if (w) {
+            unsigned rows = layer_weight_rows(&l);
+            unsigned k = l.type == LAYERNORM_LAYER ? 1 : layer_contraction_k(&l);
+            unsigned kpad = l.type == LAYERNORM_LAYER ? 1 : (unsigned)round_up(k, 32);
+            dd->kpad[i] = kpad;
+            std::vector<float> padded((size_t)rows * kpad, 0.f);
+            const float *src = (const float *)w->data;
+            for (unsigned r = 0; r < rows; r++)
+                for (unsigned c = 0; c < k; c++) {
+                    float v = src[(size_t)r * k + c];
+                    padded[(size_t)r * kpad + c] = (precision == 0 && l.type != LAYERNORM_LAYER) ? round_to_tf32(v) : v;
+                }
+            CUDA_TRY(cudaMalloc(&dd->weight[precision][i], padded.size() * sizeof(float) + 256));
+            CUDA_TRY(cudaMemcpy(dd->weight[precision][i], padded.data(), padded.size() * sizeof(float), cudaMemcpyHostToDevice));
+        }
+        if (b && !dd->bias[i]) {
+            CUDA_TRY(cudaMalloc(&dd->bias[i], (size_t)b->num_elements * sizeof(float) + 256));
+            CUDA_TRY(cudaMemcpy(dd->bias[i], b->data, (size_t)b->num_elements * sizeof(float), cudaMemcpyHostToDevice));
+        }
+        if (a && !dd->anchors[i]) {
+            CUDA_TRY(cudaMalloc(&dd->anchors[i], 8 * sizeof(float)));
+            CUDA_TRY(cudaMemcpy(dd->anchors[i], a->data, 6 * sizeof(float), cudaMemcpyHostToDevice));
+        }
+    }
+    dd->have[precision] = true;
+    return 0;
+}
+
+void engine_release_dnn(aspen_dnn_t *dnn) {
+    for (auto &dd : dnn->dev) {
+        if (!dd) continue;
+        int prev = 0;
+        cudaGetDevice(&prev);
+        cudaSetDevice(dd->device);
+        for (int p = 0; p < 2; p++)
+            for (float *ptr : dd->weight[p]) cudaFree(ptr);
+        for (float *ptr : dd->bias) cudaFree(ptr);
+        for (float *ptr : dd->anchors) cudaFree(ptr);
+        cudaSetDevice(prev);
+        delete dd;
+        dd = nullptr;
+    }
+}
+
+// ---- engine --------------------------------------------------------------------------------
+struct Engine {
+    int device = 0;
+    int precision = 0;
+    int num_sms = 0;
+    unsigned n_ctas = 0;
+    size_t smem_bytes = 0;
+    cudaStream_t stream = nullptr, side = nullptr;
+    CtrlDev *ctrl = nullptr;
+    StatusHost *status_h = nullptr;   // mapped host memory
+    StatusHost *status_d = nullptr;
+    unsigned *queue = nullptr;
+    unsigned queue_cap = 0;
+    NasmDev *nasms_d = nullptr;
+    unsigned nasms_cap = 0;
+    std::vector<nasm_t *> in_flight;
+    std::vector<nasm_t *> uploaded;   // graphs whose images (in this order) are in nasms_d
+    bool running = false;
+    unsigned long long stall_ns = 2000000000ull;
+    unsigned pipe_spins = 200000000u;
+    unsigned long long launches = 0;
+    float *xfer = nullptr;            // device staging for packed inputs / results
+    size_t xfer_bytes = 0;
+};
+
+struct DeviceNasm {
+    Engine *e = nullptr;
+    DeviceDnn *dd = nullptr;
+    float *arena = nullptr;
+    size_t arena_bytes = 0;
+    std::vector<size_t> ldata_off;
+    LayerDev *layers = nullptr;
+    TileDev *tiles = nullptr;
+    unsigned *children = nullptr, *dep = nullptr, *dep_init = nullptr, *layer_done = nullptr, *layer_tiles = nullptr, *init_ready = nullptr;
+    unsigned *layers_completed = nullptr;
+    unsigned *completed_h = nullptr, *completed_d = nullptr;   // mapped flag
+    void *wmaps = nullptr;
+    NasmDev host;        // template; tile_base / queue_base are filled per run
+    bool armed = false;  // has input, counters will be reset at the next run
+    bool ran = false;
+};
+
+static bool env_u64(const char *name, unsigned long long *out) {
+    const char *v = getenv(name);
+    if (!v || !*v) return false;
+    *out = strtoull(v, nullptr, 10);
+    return true;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device >= count) {
+        cudaGetLastError();
+        ASPEN_ERR("no CUDA device %d (%d visible); this library has no CPU execution path\n", device, count);
+        return nullptr;
+    }
+    cudaDeviceProp prop;
+    if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+        ASPEN_ERR("cannot select CUDA device %d\n", device);
+        return nullptr;
+    }
+    if (prop.major != 10) {
+        ASPEN_ERR("device %d is sm_%d%d; the kernels are built for sm_100a only\n", device, prop.major, prop.minor);
+        return nullptr;
+    }
+    Engine *e = new Engine();
+    e->device = device;
+    e->precision = precision;
+    e->num_sms = prop.multiProcessorCount;
+    unsigned long long v;
+    e->n_ctas = (unsigned)e->num_sms;
+    if (env_u64("ASPEN_B200_CTAS", &v) && v > 0 && v <= (unsigned long long)e->num_sms) e->n_ctas = (unsigned)v;
+    if (env_u64("ASPEN_B200_STALL_MS", &v) && v > 0) e->stall_ns = v * 1000000ull;
+    if (env_u64("ASPEN_B200_PIPE_SPINS", &v) && v > 0) e->pipe_spins = (unsigned)std::min<unsigned long long>(v, 0xffffffffull);
+    e->smem_bytes = (precision == 0 ? (size_t)tc::STAGES * tc::STAGE_BYTES : 0) + sizeof(tc::Shared) + 1024;
+    bool ok = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaMalloc(&e->ctrl, sizeof(CtrlDev)) == cudaSuccess && cudaMemset(e->ctrl, 0, sizeof(CtrlDev)) == cudaSuccess &&
+              cudaHostAlloc(&e->status_h, sizeof(StatusHost), cudaHostAllocMapped) == cudaSuccess &&
+              cudaHostGetDevicePointer(&e->status_d, e->status_h, 0) == cudaSuccess;
+    if (ok) {
+        memset((void *)e->status_h, 0, sizeof(StatusHost));
+        cudaError_t a = precision == 0
+            ? cudaFuncSetAttribute(sched::scheduler_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes)
+            : cudaFuncSetAttribute(sched::scheduler_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes);
+        ok = a == cudaSuccess;
+    }
+    if (ok && precision == 0 && !get_encode_fn()) { ASPEN_ERR("driver has no cuTensorMapEncodeTiled\n"); ok = false; }
+    if (!ok) {
+        ASPEN_ERR("engine_create: CUDA setup failed: %s\n", cudaGetErrorString(cudaGetLastError()));
+        engine_destroy(e);
+        return nullptr;
+    }
+    return e;
+}
+
+void engine_destroy(Engine *e) {
+    if (!e) return;
+    cudaSetDevice(e->device);
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    if (e->side) cudaStreamDestroy(e->side);
+    cudaFree(e->ctrl);
+    if (e->status_h) cudaFreeHost((void *)e->status_h);
+    cudaFree(e->queue);
+    cudaFree(e->nasms_d);
+    cudaFree(e->xfer);
+    delete e;
+}
+
+int engine_status(Engine *e) { return e ? (int)e->status_h->status : ASPEN_B200_ERR_CUDA; }
+
+template <typename T>
+static int to_device(T **dst, const std::vector<T> &src) {
+    size_t bytes = std::max<size_t>(src.size(), 1) * sizeof(T);
+    CUDA_TRY(cudaMalloc(dst, bytes));
+    if (!src.empty()) CUDA_TRY(cudaMemcpy(*dst, src.data(), src.size() * sizeof(T), cudaMemcpyHostToDevice));
+    return 0;
+}
+
+static int ensure_xfer(Engine *e, size_t bytes) {
+    if (e->xfer_bytes >= bytes) return 0;
+    cudaFree(e->xfer);
+    e->xfer = nullptr;
+    e->xfer_bytes = 0;
+    CUDA_TRY(cudaMalloc(&e->xfer, bytes));
+    e->xfer_bytes = bytes;
+    return 0;
+}
+
+// packed [W][H] <-> strided [W][ld] activation matrix
+__global__ void unpack_columns(float *dst, const float *src, unsigned H, unsigned ld, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        size_t w = i / H;
+        unsigned h = (unsigned)(i - w * H);
+        dst[w * ld + h] = src[i];
+    }
+}
+__global__ void pack_columns(float *dst, const float *src, unsigned H, unsigned ld, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        size_t w = i / H;
+        unsigned h = (unsigned)(i - w * H);
+        dst[i] = src[w * ld + h];
+    }
+}
+
+static void fill_layer(const nasm_t *nasm, const DeviceNasm *dn, unsigned i, int precision, LayerDev &L, int wmap_idx) {
+    const nasm_ldata_t &ld = nasm->ldata[i];
+    const aspen_layer_t &l = *ld.layer;
+    const unsigned *p = l.params;
+    memset(&L, 0, sizeof L);
+    L.type = l.type;
+    L.act = l.activation;
+    L.out = (float *)((char *)dn->arena + dn->ldata_off[i]);
+    L.ldc = ld.out_mat_stride; L.H = ld.out_mat_dims[OUT_H]; L.W = ld.out_mat_dims[OUT_W];
+    unsigned p0 = ld.parent_ldata_idx_arr[PARENT_0], p1 = ld.parent_ldata_idx_arr[PARENT_1];
+    if (p0 != (unsigned)-1) {
+        L.in0 = (const float *)((char *)dn->arena + dn->ldata_off[p0]);
+        L.ld0 = nasm->ldata[p0].out_mat_stride; L.H0 = nasm->ldata[p0].out_mat_dims[OUT_H];
+    }
+    if (p1 != (unsigned)-1) {
+        L.in1 = (const float *)((char *)dn->arena + dn->ldata_off[p1]);
+        L.ld1 = nasm->ldata[p1].out_mat_stride; L.H1 = nasm->ldata[p1].out_mat_dims[OUT_H];
+    }
+    L.weight = dn->dd->weight[precision][i];
+    L.bias = dn->dd->bias[i];
+    L.anchors = dn->dd->anchors[i];
+    L.rows = layer_weight_rows(&l);
+    L.K = layer_contraction_k(&l);
+    L.Kpad = dn->dd->kpad[i];
+    L.IC = p[IN_C]; L.IH = p[IN_H]; L.IW = p[IN_W]; L.OH = p[OUT_H]; L.OW = p[OUT_W];
+    L.KH = p[WEIGHT_H]; L.KW = p[WEIGHT_W]; L.stride = p[STRIDE] ? p[STRIDE] : 1; L.pad = p[PADDING];
+    if (l.type == FC_LAYER) { L.KH = p[IN_H]; L.KW = p[IN_W]; L.OH = 1; L.OW = 1; L.stride = 1; L.pad = 0; }
+    L.seq = nasm->tr_seq_len; L.heads = p[NUM_HEAD]; L.hd = p[NUM_HEAD] ? p[NUM_HIDDEN] / p[NUM_HEAD] : 0; L.masked = p[MASKED];
+    L.p_out_c = p[OUT_C]; L.p_in_c = p[IN_C]; L.p_stride = p[STRIDE];
+    L.wmap = wmap_idx;
+    switch (l.type) {
+        case CONV_LAYER: case FC_LAYER: L.a_vec4 = (L.IC % 4 == 0) && (L.ld0 % 4 == 0); break;
+        case MATMUL_LAYER: L.a_vec4 = (L.K % 4 == 0) && (L.ld0 % 4 == 0); break;
+        case K_ATTENTION_LAYER: L.a_vec4 = (L.hd % 4 == 0) && (L.ld0 % 4 == 0) && (L.ld1 % 4 == 0); break;
+        case V_ATTENTION_LAYER: L.a_vec4 = (L.seq % 4 == 0) && (L.ld0 % 4 == 0); break;
+        default: L.a_vec4 = 0; break;
+    }
+}
+
+static void free_device_nasm(DeviceNasm *dn) {
+    if (!dn) return;
+    cudaFree(dn->arena); cudaFree(dn->layers); cudaFree(dn->tiles); cudaFree(dn->children); cudaFree(dn->dep);
+    cudaFree(dn->dep_init); cudaFree(dn->layer_done); cudaFree(dn->layer_tiles); cudaFree(dn->init_ready);
+    cudaFree(dn->layers_completed); cudaFree(dn->wmaps);
+    if (dn->completed_h) cudaFreeHost(dn->completed_h);
+    delete dn;
+}
+
+static int build_device_nasm(Engine *e, nasm_t *nasm) {
+    DeviceNasm *dn = new DeviceNasm();
+    dn->e = e;
+    nasm->dev = dn;
+    if (upload_weights(nasm->dnn, e->device, e->precision, &dn->dd) != 0) return -1;
+    // activation arena: one region per layer (no reuse: every layer output stays readable)
+    dn->ldata_off.resize(nasm->num_ldata);
+    size_t off = 0;
+    for (unsigned i = 0; i < nasm->num_ldata; i++) {
+        dn->ldata_off[i] = off;
+        off += round_up(nasm->ldata[i].out_mat_mem_size + 64, 256);
+    }
+    dn->arena_bytes = off + 4096;
+    CUDA_TRY(cudaMalloc(&dn->arena, dn->arena_bytes));
+    CUDA_TRY(cudaMemsetAsync(dn->arena, 0, dn->arena_bytes, e->stream));
+
+    // layers + weight tensor maps
+    std::vector<LayerDev> layers(nasm->num_ldata);
+    std::vector<CUtensorMap> maps;
+    for (unsigned i = 0; i < nasm->num_ldata; i++) {
+        const aspen_layer_t &l = *nasm->ldata[i].layer;
+        int wmap = -1;
+        const bool gemm_w = l.type == CONV_LAYER || l.type == FC_LAYER || l.type == MATMUL_LAYER;
+        if (gemm_w && e->precision == 0) {
+            CUtensorMap m;
+            cuuint64_t dims[2] = {dn->dd->kpad[i], layer_weight_rows(&l)};
+            cuuint64_t strides[1] = {(cuuint64_t)dn->dd->kpad[i] * sizeof(float)};
+            cuuint32_t box[2] = {32, 64}, estr[2] = {1, 1};
+            CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dn->dd->weight[0][i], dims, strides, box, estr,
+                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) { ASPEN_ERR("cuTensorMapEncodeTiled failed (%d) for layer %u\n", (int)r, i); return -1; }
+            wmap = (int)maps.size();
+            maps.push_back(m);
+        }
+        fill_layer(nasm, dn, i, e->precision, layers[i], wmap);
+        if (e->precision == 0) {
+            const LayerDev &L = layers[i];
+            if (l.type == K_ATTENTION_LAYER && (!L.a_vec4 || L.seq > tc::TMEM_COLS)) {
+                ASPEN_ERR("attention_k layer %u: head size must be a multiple of 4 and seq <= %u on the tensor-core path\n", i, tc::TMEM_COLS);
+                return -1;
+            }
+        }
+    }
+    if (to_device(&dn->layers, layers) != 0) return -1;
+    {
+        size_t bytes = std::max<size_t>(maps.size(), 1) * sizeof(CUtensorMap);
+        CUDA_TRY(cudaMalloc(&dn->wmaps, bytes));
+        if (!maps.empty()) CUDA_TRY(cudaMemcpy(dn->wmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+    }
+
+    // tiles, children (CSR over true dependencies = listed parents + supplement), counters
+    const unsigned n = nasm->num_ninst;
+    std::vector<TileDev> tiles(n);
+    std::vector<std::vector<unsigned>> kids(n);
+    std::vector<unsigned> dep_init(n, 0), init_ready, layer_tiles(nasm->num_ldata);
+    const unsigned n_input = nasm->ldata[0].num_ninst;
+    for (unsigned t = 0; t < n; t++) {
+        const ninst_t &ni = nasm->ninst[t];
+        TileDev &T = tiles[t];
+        T.layer = (unsigned)(ni.ldata - nasm->ldata.data());
+        T.pos_h = ni.out_mat_pos[OUT_H]; T.pos_w = ni.out_mat_pos[OUT_W];
+        T.tile_h = ni.tile_dims[OUT_H]; T.tile_w = ni.tile_dims[OUT_W];
+        T.need = (unsigned)(ni.parent_ninst_idx.size() + ni.extra_parent_idx.size());
+        for (int pass = 0; pass < 2; pass++)
+            for (unsigned par : (pass == 0 ? ni.parent_ninst_idx : ni.extra_parent_idx)) {
+                if (par >= n || par >= t) { ASPEN_ERR("tile %u lists parent %u that does not precede it\n", t, par); return -1; }
+                kids[par].push_back(t);
+                if (par < n_input) dep_init[t]++;
+            }
+        if (t >= n_input && T.need == 0) { ASPEN_ERR("tile %u of layer %u has no parents and can never run\n", t, T.layer); return -1; }
+        if (t >= n_input && dep_init[t] == T.need) init_ready.push_back(t);
+    }
+    std::vector<unsigned> children;
+    for (unsigned t = 0; t < n; t++) {
+        tiles[t].child_off = (unsigned)children.size();
+        tiles[t].child_cnt = (unsigned)kids[t].size();
+        children.insert(children.end(), kids[t].begin(), kids[t].end());
+    }
+    for (unsigned i = 0; i < nasm->num_ldata; i++) layer_tiles[i] = nasm->ldata[i].num_ninst;
+    std::vector<unsigned> zeros(std::max(n, nasm->num_ldata), 0);
+    if (to_device(&dn->tiles, tiles) != 0 || to_device(&dn->children, children) != 0 || to_device(&dn->dep_init, dep_init) != 0 ||
+        to_device(&dn->init_ready, init_ready) != 0 || to_device(&dn->layer_tiles, layer_tiles) != 0)
+        return -1;
+    CUDA_TRY(cudaMalloc(&dn->dep, std::max<size_t>(n, 1) * sizeof(unsigned)));
+    CUDA_TRY(cudaMalloc(&dn->layer_done, nasm->num_ldata * sizeof(unsigned)));
+    CUDA_TRY(cudaMalloc(&dn->layers_completed, sizeof(unsigned)));
+    CUDA_TRY(cudaHostAlloc(&dn->completed_h, sizeof(unsigned), cudaHostAllocMapped));
+    *dn->completed_h = 0;
+    CUDA_TRY(cudaHostGetDevicePointer(&dn->completed_d, dn->completed_h, 0));
+
+    NasmDev &H = dn->host;
+    memset(&H, 0, sizeof H);
+    H.layers = dn->layers; H.tiles = dn->tiles; H.children = dn->children; H.dep = dn->dep; H.dep_init = dn->dep_init;
+    H.layer_done = dn->layer_done; H.layer_tiles = dn->layer_tiles; H.init_ready = dn->init_ready;
+    H.layers_completed = dn->layers_completed; H.completed = dn->completed_d; H.wmaps = dn->wmaps;
+    H.n_tiles = n; H.n_layers = nasm->num_ldata; H.n_init = (unsigned)init_ready.size(); H.n_input_tiles = n_input;
+    return 0;
+}
+
+int engine_set_input(nasm_t *nasm, const void *input_host) {
+    DeviceNasm *dn = nasm->dev;
+    if (!dn) return -1;
+    Engine *e = dn->e;
+    CUDA_TRY(cudaSetDevice(e->device));
+    const nasm_ldata_t &l0 = nasm->ldata[0];
+    const size_t n = (size_t)l0.out_mat_dims[OUT_H] * l0.out_mat_dims[OUT_W];
+    float *dst = (float *)((char *)dn->arena + dn->ldata_off[0]);
+    if (!input_host) {
+        CUDA_TRY(cudaMemsetAsync(dst, 0, l0.out_mat_mem_size, e->stream));
+        return 0;
+    }
+    if (l0.out_mat_stride == l0.out_mat_dims[OUT_H]) {
+        CUDA_TRY(cudaMemcpyAsync(dst, input_host, n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+    } else {
+        if (ensure_xfer(e, n * sizeof(float)) != 0) return -1;
+        CUDA_TRY(cudaMemcpyAsync(e->xfer, input_host, n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+        unsigned blocks = (unsigned)std::min<size_t>((n + 255) / 256, 4096);
+        unpack_columns<<<blocks, 256, 0, e->stream>>>(dst, e->xfer, l0.out_mat_dims[OUT_H], l0.out_mat_stride, n);
+        e->launches++;
+        CUDA_TRY(cudaGetLastError());
+    }
+    // The caller may reuse its buffer as soon as we return (the reference copies synchronously).
+    CUDA_TRY(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+int engine_attach_nasm(Engine *e, nasm_t *nasm, const void *input_host) {
+    if (!e) return -1;
+    CUDA_TRY(cudaSetDevice(e->device));
+    if (nasm->dev && nasm->dev->e != e) { engine_detach_nasm(nasm); }
+    if (!nasm->dev) {
+        if (build_device_nasm(e, nasm) != 0) { engine_detach_nasm(nasm); return -1; }
+    }
+    if (engine_set_input(nasm, input_host) != 0) return -1;
+    nasm->dev->armed = true;
+    *nasm->dev->completed_h = 0;
+    return 0;
+}
+
+void engine_detach_nasm(nasm_t *nasm) {
+    DeviceNasm *dn = nasm->dev;
+    if (!dn) return;
+    Engine *e = dn->e;
+    cudaSetDevice(e->device);
+    if (e->running) { cudaStreamSynchronize(e->stream); e->running = false; }
+    e->in_flight.erase(std::remove(e->in_flight.begin(), e->in_flight.end(), nasm), e->in_flight.end());
+    e->uploaded.clear();
+    free_device_nasm(dn);
+    nasm->dev = nullptr;
+}
+
+int engine_rearm(Engine *e, nasm_t *nasm) {
+    if (!nasm->dev) return -1;
+    if (e->running && std::find(e->in_flight.begin(), e->in_flight.end(), nasm) != e->in_flight.end()) {
+        // re-arming a graph the device is still draining: let that run finish first
+        cudaSetDevice(e->device);
+        cudaStreamSynchronize(e->stream);
+        e->running = false;
+        e->in_flight.clear();
+    }
+    nasm->dev->armed = true;
+    *nasm->dev->completed_h = 0;
+    return 0;
+}
+
+static int launch_run(Engine *e, const std::vector<nasm_t *> &run) {
+    std::vector<NasmDev> images(run.size());
+    unsigned total = 0, n_init = 0, n_input = 0;
+    for (size_t i = 0; i < run.size(); i++) {
+        DeviceNasm *dn = run[i]->dev;
+        images[i] = dn->host;
+        images[i].tile_base = total;
+        images[i].queue_base = n_init;
+        total += dn->host.n_tiles;
+        n_init += dn->host.n_init;
+        n_input += dn->host.n_input_tiles;
+    }
+    if (run.size() > e->nasms_cap) {
+        cudaFree(e->nasms_d);
+        e->nasms_d = nullptr;
+        e->nasms_cap = 0;
+        CUDA_TRY(cudaMalloc(&e->nasms_d, run.size() * sizeof(NasmDev)));
+        e->nasms_cap = (unsigned)run.size();
+    }
+    if (total > e->queue_cap) {
+        cudaFree(e->queue);
+        e->queue = nullptr;
+        e->queue_cap = 0;
+        CUDA_TRY(cudaMalloc(&e->queue, (size_t)total * sizeof(unsigned)));
+        e->queue_cap = total;
+    }
+    if (run != e->uploaded) {
+        // cudaMemcpyAsync from pageable memory returns after the source has been staged
+        CUDA_TRY(cudaMemcpyAsync(e->nasms_d, images.data(), images.size() * sizeof(NasmDev), cudaMemcpyHostToDevice, e->stream));
+        unsigned n_nasm = (unsigned)run.size();
+        CUDA_TRY(cudaMemcpyAsync(&e->ctrl->n_nasm, &n_nasm, sizeof(unsigned), cudaMemcpyHostToDevice, e->stream));
+        e->uploaded = run;
+    }
+    e->status_h->status = 0;
+    e->status_h->tiles_done = 0;
+    unsigned arm_blocks = std::min<unsigned>((total + 255) / 256, 1024);
+    sched::arm_kernel<<<arm_blocks, 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue, total, n_init, n_input, e->stall_ns, e->pipe_spins);
+    sched::seed_kernel<<<std::max(1u, std::min<unsigned>((n_init + 255) / 256, 256)), 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue);
+    if (e->precision == 0)
+        sched::scheduler_kernel<true><<<e->n_ctas, tc::NTHREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d);
+    else
+        sched::scheduler_kernel<false><<<e->n_ctas, tc::NTHREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d);
+    e->launches += 3;
+    CUDA_TRY(cudaGetLastError());
+    return 0;
+}
+
+int engine_run(Engine *e, const std::vector<nasm_t *> &nasms) {
+    if (!e) return -1;
+    CUDA_TRY(cudaSetDevice(e->device));
+    std::vector<nasm_t *> run;
+    for (nasm_t *n : nasms)
+        if (n->dev && n->dev->e == e && n->dev->armed) run.push_back(n);
+    if (run.empty()) return 0;
+    if (e->running) {   // one persistent kernel at a time per group: the armed graphs join the next launch
+        CUDA_TRY(cudaStreamSynchronize(e->stream));
+        e->running = false;
+        e->in_flight.clear();
+    }
+    if (launch_run(e, run) != 0) return -1;
+    for (nasm_t *n : run) { n->dev->armed = false; n->dev->ran = true; }
+    e->in_flight = run;
+    e->running = true;
+    return 0;
+}
+
+int engine_stop(Engine *e) {
+    if (!e || !e->running) return 0;
+    CUDA_TRY(cudaSetDevice(e->device));
+    if (cudaStreamQuery(e->stream) == cudaErrorNotReady) {
+        // cooperative stop: CTAs leave after their current tile (ref src/dse.c:215-232)
+        unsigned one = 1;
+        cudaMemcpyAsync(&e->ctrl->stop, &one, sizeof(unsigned), cudaMemcpyHostToDevice, e->side);
+    }
+    cudaError_t err = cudaStreamSynchronize(e->stream);
+    e->running = false;
+    for (nasm_t *n : e->in_flight)
+        if (n->dev && *(volatile unsigned *)n->dev->completed_h == 0) n->dev->armed = true;   // unfinished: restarts at the next run
+    e->in_flight.clear();
+    if (err != cudaSuccess) { ASPEN_ERR("CUDA error after run: %s\n", cudaGetErrorString(err)); e->status_h->status = ASPEN_B200_ERR_CUDA; return -1; }
+    return 0;
+}
+
+unsigned int engine_poll_nasm(nasm_t *nasm) { return nasm->dev ? *(volatile unsigned *)nasm->dev->completed_h : 0; }
+
+int engine_wait_nasm(nasm_t *nasm) {
+    DeviceNasm *dn = nasm->dev;
+    if (!dn) return -1;
+    Engine *e = dn->e;
+    cudaSetDevice(e->device);
+    for (unsigned spin = 0;; spin++) {
+        if (*(volatile unsigned *)dn->completed_h) return 0;
+        if (!e->running) return -1;
+        cudaError_t q = cudaStreamQuery(e->stream);
+        if (q == cudaSuccess) return *(volatile unsigned *)dn->completed_h ? 0 : -1;   // kernel left without finishing this graph
+        if (q != cudaErrorNotReady) { ASPEN_ERR("CUDA error while waiting: %s\n", cudaGetErrorString(q)); e->status_h->status = ASPEN_B200_ERR_CUDA; return -1; }
+        if (spin > 64) sched_yield();
+    }
+}
+
+long engine_read_ldata(nasm_t *nasm, unsigned int idx, float *out) {
+    DeviceNasm *dn = nasm->dev;
+    if (!dn) return -1;
+    Engine *e = dn->e;
+    if (cudaSetDevice(e->device) != cudaSuccess) return -1;
+    const nasm_ldata_t &ld = nasm->ldata[idx];
+    const size_t n = (size_t)ld.out_mat_dims[OUT_H] * ld.out_mat_dims[OUT_W];
+    const float *src = (const float *)((char *)dn->arena + dn->ldata_off[idx]);
+    if (ld.out_mat_stride == ld.out_mat_dims[OUT_H]) {
+        if (cudaMemcpyAsync(out, src, n * sizeof(float), cudaMemcpyDeviceToHost, e->stream) != cudaSuccess) return -1;
+    } else {
+        if (ensure_xfer(e, n * sizeof(float)) != 0) return -1;
+        unsigned blocks = (unsigned)std::min<size_t>((n + 255) / 256, 4096);
+        pack_columns<<<blocks, 256, 0, e->stream>>>(e->xfer, src, ld.out_mat_dims[OUT_H], ld.out_mat_stride, n);
+        e->launches++;
+        if (cudaMemcpyAsync(out, e->xfer, n * sizeof(float), cudaMemcpyDeviceToHost, e->stream) != cudaSuccess) return -1;
+    }
+    if (cudaStreamSynchronize(e->stream) != cudaSuccess) { ASPEN_ERR("CUDA error reading layer %u: %s\n", idx, cudaGetErrorString(cudaGetLastError())); return -1; }
+    return (long)n;
+}
+
+double engine_time_runs(Engine *e, const std::vector<nasm_t *> &nasms, unsigned int warmup, unsigned int iters, unsigned long long *launches) {
+    if (!e) return -1.0;
+    if (cudaSetDevice(e->device) != cudaSuccess) return -1.0;
+    cudaEvent_t t0, t1;
+    if (cudaEventCreate(&t0) != cudaSuccess || cudaEventCreate(&t1) != cudaSuccess) return -1.0;
+    unsigned long long l0 = 0;
+    std::vector<nasm_t *> run;
+    for (nasm_t *n : nasms)
+        if (n->dev && n->dev->e == e) run.push_back(n);
+    if (run.empty()) return -1.0;
+    if (e->running) { cudaStreamSynchronize(e->stream); e->running = false; e->in_flight.clear(); }
+    for (unsigned i = 0; i < warmup + iters; i++) {
+        if (i == warmup) { cudaEventRecord(t0, e->stream); l0 = e->launches; }
+        if (launch_run(e, run) != 0) return -1.0;   // back to back on one stream: arming waits for the previous run
+    }
+    cudaEventRecord(t1, e->stream);
+    cudaError_t err = cudaStreamSynchronize(e->stream);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, t0, t1);
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+    for (nasm_t *n : run) { n->dev->armed = false; n->dev->ran = true; }
+    if (launches) *launches = e->launches - l0;
+    if (err != cudaSuccess || e->status_h->status != 0) {
+        ASPEN_ERR("timed runs failed: cuda=%s engine status=%u (info %u %u)\n", cudaGetErrorString(err), e->status_h->status, e->status_h->info0, e->status_h->info1);
+        return -1.0;
+    }
+    for (nasm_t *n : run)
+        if (*(volatile unsigned *)n->dev->completed_h == 0) { ASPEN_ERR("timed runs: a graph did not complete\n"); return -1.0; }
+    return (double)ms;
+}
+
+void engine_flush() {}

@@ -1,0 +1,332 @@
+// Tile kernels that run on the CUDA cores: the memory-bound layer types (residual, pooling,
+// layernorm, softmax, yolo, append) and the fp32-FFMA validation variant of the contraction tiles.
+// Every function is executed by `nthr` cooperating threads of one CTA (thread ids 0..nthr-1) on
+// one ninst tile.  Semantics follow the reference tile kernels, src/tiled_kernels.c (cited per
+// function); activations are read with L1 bypass because other SMs produce them during the same
+// kernel.
+#pragma once
+#include "device_types.h"
+#include "../../include/aspen_b200.h"
+
+// Barrier among the worker threads of a CTA only (the control warp does not take part).
+__device__ __forceinline__ void worker_barrier(unsigned nthr) { asm volatile("bar.sync 1, %0;" ::"r"(nthr) : "memory"); }
+
+__device__ __forceinline__ float4 ldcg4(const float *p) { return __ldcg(reinterpret_cast<const float4 *>(p)); }
+__device__ __forceinline__ float ldcg1(const float *p) { return __ldcg(p); }
+
+// ref src/naive_kernels.c:11-57 (double-precision exp/tanh where the reference calls the double libm)
+__device__ __forceinline__ float activate(float x, int act) {
+    switch (act) {
+        case RELU: return x > 0.f ? x : 0.f;
+        case LEAKY_RELU: return x > 0.f ? x : (float)(0.1 * (double)x);
+        case ELU: return x > 0.f ? x : (float)(0.1 * (exp((double)x) - 1.0));
+        case SELU: return x > 0.f ? (float)(1.0507 * (double)x) : (float)(1.0507 * 1.67326 * (exp((double)x) - 1.0));
+        case SIGMOID: return (float)(1.0 / (1.0 + exp(-(double)x)));
+        case TANH: return (float)tanh((double)x);
+        case GELU: return 0.5f * x * (1.f + erff(x * 0.7071067811865475f));
+        case GELU_ACCURATE: return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+        default: return x;   // NO_ACTIVATION, LINEAR
+    }
+}
+
+// Output pixel (flattened column index) -> batch and top-left input coordinate of its window.
+struct PixelWin { int b, ih0, iw0; };
+__device__ __forceinline__ PixelWin pixel_window(const LayerDev &L, unsigned col) {
+    unsigned hw = L.OH * L.OW;
+    unsigned b = col / hw, r = col - b * hw;
+    unsigned oh = r / L.OW, ow = r - oh * L.OW;
+    PixelWin w;
+    w.b = (int)b;
+    w.ih0 = (int)(oh * L.stride) - (int)L.pad;
+    w.iw0 = (int)(ow * L.stride) - (int)L.pad;
+    return w;
+}
+// Pointer to the channel vector of input pixel (b, ih, iw), or nullptr when it is padding.
+__device__ __forceinline__ const float *input_pixel(const LayerDev &L, const PixelWin &w, int kh, int kw) {
+    int ih = w.ih0 + kh, iw = w.iw0 + kw;
+    if (ih < 0 || ih >= (int)L.IH || iw < 0 || iw >= (int)L.IW) return nullptr;
+    return L.in0 + ((size_t)(w.b * (int)L.IH + ih) * L.IW + iw) * L.ld0;
+}
+
+// ref src/tiled_kernels.c:613-638
+__device__ void tile_residual(const LayerDev &L, const TileDev &T, unsigned tid, unsigned nthr) {
+    const unsigned h4 = T.tile_h >> 2, per_col = h4 + (T.tile_h & 3);
+    for (unsigned i = tid; i < T.tile_w * per_col; i += nthr) {
+        unsigned n = i / per_col, j = i - n * per_col;
+        size_t col = T.pos_w + n;
+        if (j < h4) {
+            unsigned m = T.pos_h + 4 * j;
+            float4 a = ldcg4(L.in0 + col * L.ld0 + m), b = ldcg4(L.in1 + col * L.ld1 + m);
+            float4 o = {activate(a.x + b.x, L.act), activate(a.y + b.y, L.act), activate(a.z + b.z, L.act), activate(a.w + b.w, L.act)};
+            *reinterpret_cast<float4 *>(L.out + col * L.ldc + m) = o;
+        } else {
+            unsigned m = T.pos_h + 4 * h4 + (j - h4);
+            L.out[col * L.ldc + m] = activate(ldcg1(L.in0 + col * L.ld0 + m) + ldcg1(L.in1 + col * L.ld1 + m), L.act);
+        }
+    }
+}
+
+// ref src/tiled_kernels.c:411-501.  Max ignores padded taps (all padded -> -inf); average divides by
+// the full window size, padding counted.
+template <bool IS_MAX>
+__device__ void tile_pool(const LayerDev &L, const TileDev &T, unsigned tid, unsigned nthr) {
+    const unsigned h4 = T.tile_h >> 2, per_col = h4 + (T.tile_h & 3);
+    const float inv = 1.f / (float)(L.KH * L.KW);
+    for (unsigned i = tid; i < T.tile_w * per_col; i += nthr) {
+        unsigned n = i / per_col, j = i - n * per_col;
+        size_t col = T.pos_w + n;
+        PixelWin w = pixel_window(L, (unsigned)col);
+        bool vec = j < h4;
+        unsigned m = T.pos_h + (vec ? 4 * j : 4 * h4 + (j - h4));
+        const float init = IS_MAX ? -INFINITY : 0.f;
+        float4 acc = {init, init, init, init};
+        for (int kh = 0; kh < (int)L.KH; kh++)
+            for (int kw = 0; kw < (int)L.KW; kw++) {
+                const float *src = input_pixel(L, w, kh, kw);
+                if (!src) continue;
+                float4 v;
+                if (vec) v = ldcg4(src + m);
+                else { v.x = ldcg1(src + m); v.y = v.z = v.w = 0.f; }
+                if (IS_MAX) { acc.x = acc.x >= v.x ? acc.x : v.x; acc.y = acc.y >= v.y ? acc.y : v.y; acc.z = acc.z >= v.z ? acc.z : v.z; acc.w = acc.w >= v.w ? acc.w : v.w; }
+                else { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+            }
+        if (!IS_MAX) { acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv; }
+        if (vec) {
+            float4 o = {activate(acc.x, L.act), activate(acc.y, L.act), activate(acc.z, L.act), activate(acc.w, L.act)};
+            *reinterpret_cast<float4 *>(L.out + col * L.ldc + m) = o;
+        } else {
+            L.out[col * L.ldc + m] = activate(acc.x, L.act);
+        }
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ref src/tiled_kernels.c:743-783: one pass mean / E[x^2], eps 1e-6, gain and shift.  One warp per column.
+__device__ void tile_layernorm(const LayerDev &L, const TileDev &T, unsigned tid, unsigned nthr) {
+    const unsigned warp = tid >> 5, lane = tid & 31, nwarp = nthr >> 5;
+    const unsigned M = T.tile_h;
+    const float *gain = L.weight + T.pos_h;
+    const float *shift = L.bias ? L.bias + T.pos_h : nullptr;
+    for (unsigned n = warp; n < T.tile_w; n += nwarp) {
+        const float *x = L.in0 + (size_t)(T.pos_w + n) * L.ld0 + T.pos_h;
+        float *y = L.out + (size_t)(T.pos_w + n) * L.ldc + T.pos_h;
+        float s = 0.f, ss = 0.f;
+        const unsigned M4 = M & ~3u;
+        for (unsigned m = lane * 4; m < M4; m += 128) {
+            float4 v = ldcg4(x + m);
+            s += v.x + v.y + v.z + v.w;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        for (unsigned m = M4 + lane; m < M; m += 32) { float v = ldcg1(x + m); s += v; ss += v * v; }
+        s = warp_sum(s);
+        ss = warp_sum(ss);
+        float mean = s / (float)M;
+        float var = ss / (float)M - mean * mean;
+        float inv = 1.f / sqrtf(var + 1e-6f);
+        for (unsigned m = lane * 4; m < M4; m += 128) {
+            float4 v = ldcg4(x + m);
+            float4 g = *reinterpret_cast<const float4 *>(gain + m);
+            float4 o = {(v.x - mean) * inv * g.x, (v.y - mean) * inv * g.y, (v.z - mean) * inv * g.z, (v.w - mean) * inv * g.w};
+            if (shift) { float4 b = *reinterpret_cast<const float4 *>(shift + m); o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w; }
+            *reinterpret_cast<float4 *>(y + m) = o;
+        }
+        for (unsigned m = M4 + lane; m < M; m += 32) {
+            float o = (ldcg1(x + m) - mean) * inv * gain[m];
+            if (shift) o += shift[m];
+            y[m] = o;
+        }
+    }
+}
+
+// ref src/tiled_kernels.c:640-673: max-subtracted softmax down each column.  One warp per column.
+__device__ void tile_softmax(const LayerDev &L, const TileDev &T, unsigned tid, unsigned nthr) {
+    const unsigned warp = tid >> 5, lane = tid & 31, nwarp = nthr >> 5;
+    const unsigned M = T.tile_h;
+    for (unsigned n = warp; n < T.tile_w; n += nwarp) {
+        const float *x = L.in0 + (size_t)(T.pos_w + n) * L.ld0 + T.pos_h;
+        float *y = L.out + (size_t)(T.pos_w + n) * L.ldc + T.pos_h;
+        float mx = -INFINITY;
+        for (unsigned m = lane; m < M; m += 32) mx = fmaxf(mx, ldcg1(x + m));
+        mx = warp_max(mx);
+        float s = 0.f;
+        for (unsigned m = lane; m < M; m += 32) s += expf(ldcg1(x + m) - mx);
+        s = warp_sum(s);
+        for (unsigned m = lane; m < M; m += 32) y[m] = expf(ldcg1(x + m) - mx) / s;
+    }
+}
+
+// ref src/tiled_kernels.c:675-709: box decode of one detection head.
+__device__ void tile_yolo(const LayerDev &L, const TileDev &T, unsigned tid, unsigned nthr) {
+    const unsigned C = L.p_out_c;
+    const unsigned a_num = L.p_in_c / C, hw = L.IH * L.IW;
+    for (unsigned i = tid; i < T.tile_w * C; i += nthr) {
+        unsigned n = i / C, j = i - n * C;
+        unsigned w_pos = T.pos_w + n;
+        unsigned bidx = w_pos / (hw * a_num), b_num = w_pos % (hw * a_num);
+        unsigned aidx = b_num / hw, wh = b_num % hw;
+        unsigned hidx = wh / L.IW, widx = wh % L.IW;
+        unsigned cidx = T.pos_h + aidx * C;
+        const float *in = L.in0 + (size_t)(bidx * hw + hidx * L.IW + widx) * L.ld0 + cidx;
+        float *out = L.out + (size_t)w_pos * L.ldc + T.pos_h;
+        float v = ldcg1(in + j), o;
+        if (j == 0) o = (1.0f / (1.0f + expf(-v)) + (float)widx) * (float)L.p_stride;
+        else if (j == 1) o = (1.0f / (1.0f + expf(-v)) + (float)hidx) * (float)L.p_stride;
+        else if (j == 2) o = expf(v) * L.anchors[2 * aidx];
+        else if (j == 3) o = expf(v) * L.anchors[2 * aidx + 1];
+        else o = 1.0f / (1.0f + expf(-v));
+        out[j] = o;
+    }
+}
+
+// ref src/tiled_kernels.c:711-741: nearest-neighbour upsample of PARENT_0 concatenated with PARENT_1.
+__device__ void tile_append(const LayerDev &L, const TileDev &T, unsigned tid, unsigned nthr) {
+    const unsigned c1 = L.p_in_c, c2 = L.p_out_c - L.p_in_c, C = c1 + c2;
+    const unsigned w2 = L.OW, w1 = L.IW, s = L.p_stride;
+    for (unsigned i = tid; i < T.tile_w * C; i += nthr) {
+        unsigned n = i / C, c = i - n * C;
+        unsigned w_pos = T.pos_w + n;
+        unsigned widx2 = w_pos % w2, hidx2 = w_pos / w2;
+        unsigned widx1 = widx2 / s, hidx1 = hidx2 / s;
+        float v = c < c1 ? ldcg1(L.in0 + (size_t)(hidx1 * w1 + widx1) * L.ld0 + c)
+                         : ldcg1(L.in1 + (size_t)(hidx2 * w2 + widx2) * L.ld1 + (c - c1));
+        L.out[(size_t)w_pos * L.ldc + c] = v;
+    }
+}
+
+// ---- fp32 FFMA contraction tiles (validation mode) -----------------------------------------
+// out[col n][row m] = epilogue( sum_k  W(m, k) * X(n, k) ), fp32 multiply-add in k order.
+//   conv     ref src/tiled_kernels.c:161-297   X(n,k): input pixel taps (kh, kw, ic), zero padding
+//   matmul   ref src/tiled_kernels.c:299-409   X(n,k): parent column n
+//   connected ref src/tiled_kernels.c:502-612  X(n,k): flattened sample n
+//   k-attn   ref src/tiled_kernels.c:784-932   W = keys, X = queries of one (batch, head); then
+//                                              mask (-1e10), scale 1/sqrt(hd), exp, column normalise
+//   v-attn   ref src/tiled_kernels.c:934-1038  W(m,k) = V[token k][feature m], X = probabilities
+struct GemmView {
+    const float *wbase;   // row m of W starts at wbase + m * wld (k contiguous) unless w_transposed
+    size_t wld;
+    bool w_transposed;    // v-attn: W(m,k) = wbase[k * wld + m]
+    const float *xbase;   // non-conv: row n of X starts at xbase + n * xld
+    size_t xld;
+    unsigned K;
+    bool conv;
+};
+
+__device__ __forceinline__ GemmView gemm_view(const LayerDev &L, const TileDev &T) {
+    GemmView g;
+    g.conv = false; g.w_transposed = false;
+    switch (L.type) {
+        case CONV_LAYER:
+            g.wbase = L.weight + (size_t)T.pos_h * L.Kpad; g.wld = L.Kpad; g.xbase = L.in0; g.xld = L.ld0; g.K = L.K; g.conv = true;
+            break;
+        case MATMUL_LAYER:
+            g.wbase = L.weight + (size_t)T.pos_h * L.Kpad; g.wld = L.Kpad; g.xbase = L.in0 + (size_t)T.pos_w * L.ld0; g.xld = L.ld0; g.K = L.K;
+            break;
+        case FC_LAYER:   // a convolution whose window is the whole input image (geometry set at upload)
+            g.wbase = L.weight + (size_t)T.pos_h * L.Kpad; g.wld = L.Kpad; g.xbase = L.in0; g.xld = L.ld0; g.K = L.K; g.conv = true;
+            break;
+        case K_ATTENTION_LAYER: {
+            unsigned b = T.pos_w / (L.seq * L.heads), head = (T.pos_w % (L.seq * L.heads)) / L.seq, q0 = T.pos_w % L.seq;
+            g.wbase = L.in1 + (size_t)(b * L.seq + T.pos_h) * L.ld1 + head * L.hd; g.wld = L.ld1;
+            g.xbase = L.in0 + (size_t)(b * L.seq + q0) * L.ld0 + head * L.hd; g.xld = L.ld0; g.K = L.hd;
+            break;
+        }
+        default: {   // V_ATTENTION_LAYER
+            unsigned b = T.pos_w / L.seq, head = T.pos_h / L.hd, q0 = T.pos_w % L.seq;
+            g.wbase = L.in1 + (size_t)b * L.seq * L.ld1 + T.pos_h; g.wld = L.ld1; g.w_transposed = true;
+            g.xbase = L.in0 + (size_t)((b * L.heads + head) * L.seq + q0) * L.ld0; g.xld = L.ld0; g.K = L.seq;
+            break;
+        }
+    }
+    return g;
+}
+
+__device__ void tile_gemm_ffma(const LayerDev &L, const TileDev &T, unsigned tid, unsigned nthr) {
+    const GemmView g = gemm_view(L, T);
+    const unsigned mg = (T.tile_h + 3) >> 2;             // groups of 4 output rows
+    const bool vec = !g.w_transposed && (g.conv ? (L.IC & 3) == 0 : (g.K & 3) == 0) && L.a_vec4;
+    const bool is_k = L.type == K_ATTENTION_LAYER;
+    const float scale = is_k ? sqrtf((float)L.hd) : 1.f;
+    const unsigned q0 = is_k ? T.pos_w % L.seq : 0;
+    for (unsigned i = tid; i < mg * T.tile_w; i += nthr) {
+        const unsigned n = i % T.tile_w, m0 = (i / T.tile_w) * 4;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const float *w[4];
+        for (int r = 0; r < 4; r++) {
+            unsigned m = m0 + r < T.tile_h ? m0 + r : T.tile_h - 1;   // clamp: duplicates are discarded below
+            w[r] = g.w_transposed ? g.wbase + m : g.wbase + (size_t)m * g.wld;
+        }
+        if (g.conv) {
+            PixelWin pw = pixel_window(L, T.pos_w + n);
+            unsigned k = 0;
+            for (int kh = 0; kh < (int)L.KH; kh++)
+                for (int kw = 0; kw < (int)L.KW; kw++, k += L.IC) {
+                    const float *x = input_pixel(L, pw, kh, kw);
+                    if (!x) continue;
+                    if (vec) {
+                        for (unsigned c = 0; c < L.IC; c += 4) {
+                            float4 xv = ldcg4(x + c);
+                            for (int r = 0; r < 4; r++) {
+                                float4 wv = *reinterpret_cast<const float4 *>(w[r] + k + c);
+                                acc[r] = fmaf(wv.x, xv.x, acc[r]); acc[r] = fmaf(wv.y, xv.y, acc[r]);
+                                acc[r] = fmaf(wv.z, xv.z, acc[r]); acc[r] = fmaf(wv.w, xv.w, acc[r]);
+                            }
+                        }
+                    } else {
+                        for (unsigned c = 0; c < L.IC; c++) {
+                            float xv = ldcg1(x + c);
+                            for (int r = 0; r < 4; r++) acc[r] = fmaf(w[r][k + c], xv, acc[r]);
+                        }
+                    }
+                }
+        } else {
+            const float *x = g.xbase + (size_t)n * g.xld;
+            if (vec) {
+                for (unsigned k = 0; k < g.K; k += 4) {
+                    float4 xv = ldcg4(x + k);
+                    for (int r = 0; r < 4; r++) {
+                        float4 wv = ldcg4(w[r] + k);
+                        acc[r] = fmaf(wv.x, xv.x, acc[r]); acc[r] = fmaf(wv.y, xv.y, acc[r]);
+                        acc[r] = fmaf(wv.z, xv.z, acc[r]); acc[r] = fmaf(wv.w, xv.w, acc[r]);
+                    }
+                }
+            } else {
+                for (unsigned k = 0; k < g.K; k++) {
+                    float xv = ldcg1(x + k);
+                    for (int r = 0; r < 4; r++) acc[r] = fmaf(ldcg1(g.w_transposed ? w[r] + (size_t)k * g.wld : w[r] + k), xv, acc[r]);
+                }
+            }
+        }
+        float *o = L.out + (size_t)(T.pos_w + n) * L.ldc + T.pos_h + m0;
+        for (int r = 0; r < 4; r++) {
+            if (m0 + r >= T.tile_h) break;
+            float v = acc[r];
+            if (is_k) {
+                if (L.masked && (T.pos_h + m0 + r) > (q0 + n)) v = -1e10f;
+                v = expf(v / scale);
+            } else if (L.type != V_ATTENTION_LAYER) {
+                if (L.bias) v += L.bias[T.pos_h + m0 + r];
+                v = activate(v, L.act);
+            }
+            o[r] = v;
+        }
+    }
+    if (is_k) {   // normalise every column by its sum (no max subtraction, as the reference)
+        worker_barrier(nthr);
+        const unsigned warp = tid >> 5, lane = tid & 31, nwarp = nthr >> 5;
+        for (unsigned n = warp; n < T.tile_w; n += nwarp) {
+            float *o = L.out + (size_t)(T.pos_w + n) * L.ldc + T.pos_h;
+            float s = 0.f;
+            for (unsigned m = lane; m < T.tile_h; m += 32) s += ldcg1(o + m);
+            s = warp_sum(s);
+            for (unsigned m = lane; m < T.tile_h; m += 32) o[m] = ldcg1(o + m) / s;
+        }
+    }
+}

@@ -1,0 +1,401 @@
+// Contraction tiles on the 5th-generation tensor cores (sm_100a): conv, matmul, connected,
+// K-attention and V-attention ninst tiles as TF32 tcgen05.mma with fp32 accumulators in TMEM.
+//
+// Orientation.  A ninst tile is out[column n][row m] (n: pixels / tokens, m: channels / keys /
+// features, m contiguous in memory).  The MMA is issued as D[128 x N] with
+//     MMA-M (128 TMEM lanes)  <- 128 consecutive tile columns n   (operand "X": activations)
+//     MMA-N (<=256 TMEM cols) <- tile rows m                      (operand "W": weights / keys / V)
+// so each epilogue thread owns one output column n and writes runs of contiguous m, and the
+// K-attention softmax (a reduction over m) stays inside one thread.
+//
+// Staging.  Both operands are K-major, 32 fp32 (128 bytes) per row and k-chunk, in the 128-byte
+// swizzled shared-memory layout UMMA descriptors and TMA share:
+//     byte(row r, 16-byte piece c) = r * 128 + ((c ^ (r & 7)) << 4),   stage base 1024-byte aligned.
+// Weights arrive by TMA (one 64-row box per 8 KB) straight from the [rows][Kpad] device copy.
+// Activations are gathered by the worker threads with cp.async (zero-fill for padding taps and
+// k >= K) -- this is the im2col-free part: a conv tile reads pixel (b, oh*s+kh-p, ow*s+kw-p)
+// directly from the NHWC parent matrix.  cp.async writes go through the generic proxy, so a
+// thread waits for its own copies, issues fence.proxy.async and only then arrives on the stage's
+// "full" mbarrier, two stages behind its newest copy.
+//
+// Roles in the CTA: NW worker threads (gather + epilogue), one TMA thread, one MMA thread.
+// Every wait is bounded: when a spin budget runs out the thread records an error, raises the
+// abort flag and keeps walking the loop nest without touching barriers' data, so the CTA still
+// reaches its bar.sync points and exits.
+#pragma once
+#include "tiles_simt.cuh"
+
+namespace tc {
+
+constexpr int STAGES = 4;
+constexpr int LAG = 2;                       // cp.async groups a worker keeps in flight
+constexpr unsigned A_STAGE_BYTES = 128 * 128;
+constexpr unsigned B_STAGE_BYTES = 256 * 128;
+constexpr unsigned STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr unsigned NW = 256;                 // worker threads
+constexpr unsigned TMA_THREAD = NW;          // lane 0 of warp 8
+constexpr unsigned MMA_THREAD = NW + 32;     // lane 0 of warp 9
+constexpr unsigned NTHREADS = NW + 64;
+constexpr unsigned TMEM_COLS = 512;
+
+struct Shared {
+    unsigned long long full[STAGES];
+    unsigned long long empty[STAGES];
+    unsigned long long accum;
+    unsigned tmem_base;
+    unsigned tile;            // scheduler mailbox
+    float partial[NW];        // K-attention row sums of the two column halves
+};
+
+struct PipeState {            // identical in every thread, carried across tiles
+    unsigned it = 0;          // k-chunk iterations issued so far
+    unsigned acc_phase = 0;   // accumulator barrier phase
+    bool dead = false;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long *bar, unsigned bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and marks the run aborted) when the budget runs out.
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity, CtrlDev *ctrl, StatusHost *status, unsigned where) {
+    const unsigned budget = ctrl->pipe_spins;
+    for (unsigned spin = 0; spin < budget; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u && *(volatile unsigned *)&ctrl->abort) return false;
+    }
+    if (atomicCAS(&ctrl->abort, 0u, (unsigned)ASPEN_B200_ERR_PIPE) == 0u) {
+        status->info0 = where;
+        status->info1 = blockIdx.x;
+        status->status = ASPEN_B200_ERR_PIPE;
+        __threadfence_system();
+    }
+    return false;
+}
+
+__device__ __forceinline__ void cp_async16(unsigned dst, const void *src, unsigned src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(unsigned dst, const void *src, unsigned src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const void *tmap, int x, int y, unsigned long long *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(unsigned *holder, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned long long *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float *v) {
+    unsigned *r = reinterpret_cast<unsigned *>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128-byte swizzle, 8-row groups 1024 bytes apart; version 1 (sm_100) in bits 46-47.
+__device__ __forceinline__ unsigned long long umma_desc(unsigned smem_addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((smem_addr & 0x3ffffu) >> 4);
+    d |= (unsigned long long)1 << 16;                 // leading byte offset (unused for swizzled K-major)
+    d |= (unsigned long long)(1024 >> 4) << 32;       // stride byte offset
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+// D fp32, A/B tf32, both K-major, M = 128, N = n.
+__device__ __forceinline__ unsigned umma_idesc(unsigned n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ unsigned swz(unsigned row, unsigned piece) { return row * 128u + ((piece ^ (row & 7u)) << 4); }
+
+// ---- per-layer operand description -------------------------------------------------------------
+struct Operands {
+    // X (activation) side
+    const float *xrow;        // row-pointer kinds: start of column 0 of the tile; row n at xrow + n * xld
+    size_t xld;
+    bool conv;                // taps gathered from L.in0
+    // W side
+    bool tma;                 // weights by TMA
+    bool transposed;          // V-attention: W(m,k) = wbase[k * wld + m]
+    const float *wbase;       // gathered kinds: row m at wbase + m * wld
+    size_t wld;
+    unsigned w_rows;          // rows that exist (others read as zero)
+    unsigned K, Kpad;
+    bool softmax;             // K-attention epilogue
+    bool plain;               // V-attention epilogue: no bias / activation
+    unsigned q0;              // K-attention: query index of tile column 0
+};
+
+__device__ __forceinline__ Operands make_operands(const LayerDev &L, const TileDev &T) {
+    Operands o;
+    o.conv = false; o.tma = false; o.transposed = false; o.softmax = false; o.plain = false; o.q0 = 0;
+    o.xrow = nullptr; o.xld = 0; o.wbase = nullptr; o.wld = 0; o.w_rows = T.tile_h;
+    switch (L.type) {
+        case CONV_LAYER: case FC_LAYER:
+            o.conv = true; o.tma = true; o.K = L.K; o.Kpad = L.Kpad;
+            break;
+        case MATMUL_LAYER:
+            o.xrow = L.in0 + (size_t)T.pos_w * L.ld0; o.xld = L.ld0; o.tma = true; o.K = L.K; o.Kpad = L.Kpad;
+            break;
+        case K_ATTENTION_LAYER: {
+            unsigned b = T.pos_w / (L.seq * L.heads), head = (T.pos_w % (L.seq * L.heads)) / L.seq;
+            o.q0 = T.pos_w % L.seq;
+            o.xrow = L.in0 + (size_t)(b * L.seq + o.q0) * L.ld0 + head * L.hd; o.xld = L.ld0;
+            o.wbase = L.in1 + (size_t)(b * L.seq + T.pos_h) * L.ld1 + head * L.hd; o.wld = L.ld1;
+            o.K = L.hd; o.Kpad = (L.hd + 31u) & ~31u; o.softmax = true;
+            break;
+        }
+        default: {   // V_ATTENTION_LAYER
+            unsigned b = T.pos_w / L.seq, head = T.pos_h / L.hd, q0 = T.pos_w % L.seq;
+            o.xrow = L.in0 + (size_t)((b * L.heads + head) * L.seq + q0) * L.ld0; o.xld = L.ld0;
+            o.wbase = L.in1 + (size_t)b * L.seq * L.ld1 + T.pos_h; o.wld = L.ld1; o.transposed = true;
+            o.K = L.seq; o.Kpad = (L.seq + 31u) & ~31u; o.plain = true;
+            break;
+        }
+    }
+    return o;
+}
+
+// One ninst tile.  Called by all NTHREADS threads of the CTA.
+__device__ void tile_gemm(const LayerDev &L, const TileDev &T, const NasmDev &G, unsigned char *stage_mem, Shared *sh,
+                          PipeState &ps, CtrlDev *ctrl, StatusHost *status) {
+    const unsigned tid = threadIdx.x;
+    const bool is_worker = tid < NW;
+    const unsigned row = tid & 127u, half = (tid >> 7) & 1u;
+    const Operands op = make_operands(L, T);
+    const unsigned stage_base = smem_u32(stage_mem);
+    const unsigned tmem = sh->tmem_base;
+    const void *tmap = op.tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.wmap * 128) : nullptr;
+    const bool vec_x = L.a_vec4 != 0;
+
+    for (unsigned n0 = 0; n0 < T.tile_w; n0 += 128) {
+        const unsigned rows_valid = min(128u, T.tile_w - n0);
+        const bool row_ok = row < rows_valid;
+        PixelWin pw = {0, 0, 0};
+        const float *xr = nullptr;
+        if (is_worker && row_ok) {
+            if (op.conv) pw = pixel_window(L, T.pos_w + n0 + row);
+            else xr = op.xrow + (size_t)(n0 + row) * op.xld;
+        }
+        for (unsigned ms = 0; ms < T.tile_h; ms += TMEM_COLS) {
+            const unsigned cols_super = min(TMEM_COLS, T.tile_h - ms);
+            unsigned arrived = ps.it;            // next iteration this worker still owes a "full" arrival for
+            for (unsigned mp = 0; mp < cols_super; mp += 256) {
+                const unsigned nb = min(256u, cols_super - mp);
+                const unsigned NB = op.tma ? ((nb + 63u) & ~63u) : ((nb + 15u) & ~15u);
+                for (unsigned kc = 0; kc < op.Kpad; kc += 32, ps.it++) {
+                    const unsigned s = ps.it % STAGES, ph = (ps.it / STAGES) & 1u;
+                    const unsigned sA = stage_base + s * STAGE_BYTES, sB = sA + A_STAGE_BYTES;
+                    if (is_worker) {
+                        if (!ps.dead && !mbar_wait(&sh->empty[s], ph ^ 1u, ctrl, status, 1)) ps.dead = true;
+                        ps.dead = __any_sync(0xffffffffu, ps.dead);   // keep worker warps convergent on the failure path
+                        if (!ps.dead) {
+                            // ---- X side: this thread's half (4 pieces / 16 elements) of its row ----
+                            if (row_ok) {
+                                if (vec_x) {
+                                    #pragma unroll
+                                    for (unsigned c = 0; c < 4; c++) {
+                                        const unsigned piece = half * 4 + c, k = kc + piece * 4;
+                                        const float *src = L.in0;
+                                        unsigned bytes = 0;
+                                        if (k < op.K) {
+                                            if (op.conv) {
+                                                unsigned tap = k / L.IC, ic = k - tap * L.IC;
+                                                const float *px = input_pixel(L, pw, (int)(tap / L.KW), (int)(tap % L.KW));
+                                                if (px) { src = px + ic; bytes = 16; }
+                                            } else { src = xr + k; bytes = 16; }
+                                        }
+                                        cp_async16(sA + swz(row, piece), src, bytes);
+                                    }
+                                } else {
+                                    for (unsigned e = 0; e < 16; e++) {
+                                        const unsigned kk = half * 16 + e, k = kc + kk;
+                                        const float *src = L.in0;
+                                        unsigned bytes = 0;
+                                        if (k < op.K) {
+                                            if (op.conv) {
+                                                unsigned tap = k / L.IC, ic = k - tap * L.IC;
+                                                const float *px = input_pixel(L, pw, (int)(tap / L.KW), (int)(tap % L.KW));
+                                                if (px) { src = px + ic; bytes = 4; }
+                                            } else { src = xr + k; bytes = 4; }
+                                        }
+                                        cp_async4(sA + swz(row, kk >> 2) + (kk & 3u) * 4u, src, bytes);
+                                    }
+                                }
+                            }
+                            // ---- W side when it is not a TMA operand ----
+                            if (!op.tma) {
+                                if (!op.transposed) {
+                                    for (unsigned i = tid; i < NB * 8; i += NW) {
+                                        const unsigned r = i >> 3, piece = i & 7u, k = kc + piece * 4, m = ms + mp + r;
+                                        const bool ok = m < op.w_rows && k < op.K;
+                                        cp_async16(sB + swz(r, piece), ok ? op.wbase + (size_t)m * op.wld + k : L.in1, ok ? 16u : 0u);
+                                    }
+                                } else {
+                                    for (unsigned i = tid; i < NB * 32; i += NW) {
+                                        const unsigned r = i % NB, kk = i / NB, k = kc + kk, m = ms + mp + r;
+                                        const bool ok = m < op.w_rows && k < op.K;
+                                        cp_async4(sB + swz(r, kk >> 2) + (kk & 3u) * 4u, ok ? op.wbase + (size_t)k * op.wld + m : L.in1, ok ? 4u : 0u);
+                                    }
+                                }
+                            }
+                        }
+                        cp_async_commit();
+                        if (ps.it - arrived >= (unsigned)LAG) {       // copies of iteration `arrived` have landed
+                            cp_async_wait<LAG>();
+                            fence_proxy_async_smem();
+                            if (!ps.dead) mbar_arrive(&sh->full[arrived % STAGES]);
+                            arrived++;
+                        }
+                    } else if (tid == TMA_THREAD) {
+                        if (!ps.dead && !mbar_wait(&sh->empty[s], ph ^ 1u, ctrl, status, 2)) ps.dead = true;
+                        if (!ps.dead) {
+                            if (op.tma) {
+                                mbar_arrive_expect_tx(&sh->full[s], NB * 128u);
+                                for (unsigned j = 0; j < NB; j += 64)
+                                    tma_load_2d(sB + j * 128u, tmap, (int)kc, (int)(T.pos_h + ms + mp + j), &sh->full[s]);
+                            } else {
+                                mbar_arrive(&sh->full[s]);
+                            }
+                        }
+                    } else if (tid == MMA_THREAD) {
+                        if (!ps.dead && !mbar_wait(&sh->full[s], ph, ctrl, status, 3)) ps.dead = true;
+                        if (!ps.dead) {
+                            tc_fence_after();
+                            const unsigned long long adesc = umma_desc(sA), bdesc = umma_desc(sB);
+                            const unsigned idesc = umma_idesc(NB);
+                            #pragma unroll
+                            for (unsigned k8 = 0; k8 < 4; k8++)
+                                tc_mma_tf32(tmem + mp, adesc + 2ull * k8, bdesc + 2ull * k8, idesc, (kc | k8) != 0u);
+                            tc_commit(&sh->empty[s]);
+                        }
+                    }
+                }
+            }
+            // ---- all k-chunks of this 128 x cols_super block are issued ----
+            if (tid == MMA_THREAD && !ps.dead) tc_commit(&sh->accum);
+            if (is_worker) {
+                cp_async_wait<0>();
+                fence_proxy_async_smem();
+                for (; arrived != ps.it; arrived++)
+                    if (!ps.dead) mbar_arrive(&sh->full[arrived % STAGES]);
+                if (!ps.dead && !mbar_wait(&sh->accum, ps.acc_phase, ctrl, status, 4)) ps.dead = true;
+                ps.dead = __any_sync(0xffffffffu, ps.dead);
+                tc_fence_after();
+                // ---- epilogue: thread = output column n0 + row, this half's 32-wide row chunks ----
+                const unsigned lane_base = ((tid >> 5) & 3u) * 32u;
+                const unsigned nchunk = (cols_super + 31u) >> 5;
+                float *ocol = L.out + (size_t)(T.pos_w + n0 + row) * L.ldc + T.pos_h + ms;
+                float v[32];
+                if (op.softmax) {
+                    // scores -> mask -> / sqrt(hd) -> exp, normalised by the column sum (ref src/tiled_kernels.c:859-876)
+                    const float scale = sqrtf((float)L.hd);
+                    const unsigned q = op.q0 + n0 + row;
+                    float sum = 0.f;
+                    for (unsigned c = half; c < nchunk; c += 2) {
+                        if (!ps.dead) tmem_ld32(tmem + (lane_base << 16) + c * 32u, v);
+                        #pragma unroll
+                        for (unsigned j = 0; j < 32; j++) {
+                            const unsigned m = ms + c * 32u + j;
+                            if (m < T.tile_h) {
+                                float x = (L.masked && (T.pos_h + m) > q) ? -1e10f : v[j];
+                                sum += expf(x / scale);
+                            }
+                        }
+                    }
+                    sh->partial[tid] = sum;
+                    worker_barrier(NW);
+                    sum = sh->partial[row] + sh->partial[row + 128u];
+                    for (unsigned c = half; c < nchunk; c += 2) {
+                        if (!ps.dead) tmem_ld32(tmem + (lane_base << 16) + c * 32u, v);
+                        #pragma unroll
+                        for (unsigned j = 0; j < 32; j++) {
+                            const unsigned m = ms + c * 32u + j;
+                            float x = (L.masked && (T.pos_h + m) > q) ? -1e10f : v[j];
+                            v[j] = expf(x / scale) / sum;
+                        }
+                        if (row_ok && !ps.dead) {
+                            #pragma unroll
+                            for (unsigned j = 0; j < 32; j++)
+                                if (ms + c * 32u + j < T.tile_h) ocol[c * 32u + j] = v[j];
+                        }
+                    }
+                    worker_barrier(NW);   // partial[] is reused by the next block
+                } else {
+                    const float *bias = (!op.plain && L.bias) ? L.bias + T.pos_h + ms : nullptr;
+                    for (unsigned c = half; c < nchunk; c += 2) {
+                        if (!ps.dead) tmem_ld32(tmem + (lane_base << 16) + c * 32u, v);
+                        const unsigned valid = min(32u, cols_super - c * 32u);
+                        if (!op.plain) {
+                            #pragma unroll
+                            for (unsigned j = 0; j < 32; j++) {
+                                float x = v[j];
+                                if (bias && j < valid) x += __ldg(bias + c * 32u + j);
+                                v[j] = activate(x, L.act);
+                            }
+                        }
+                        if (row_ok && !ps.dead) {
+                            if (valid == 32u) {
+                                #pragma unroll
+                                for (unsigned j = 0; j < 32; j += 4)
+                                    *reinterpret_cast<float4 *>(ocol + c * 32u + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            } else {
+                                #pragma unroll
+                                for (unsigned j = 0; j < 32; j++)
+                                    if (j < valid) ocol[c * 32u + j] = v[j];
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+            }
+            ps.acc_phase ^= 1u;
+            // The MMA thread must not overwrite the accumulators before every epilogue thread has read them.
+            __syncwarp();
+            asm volatile("bar.sync 2, %0;" ::"r"(NTHREADS) : "memory");
+            if (tid == MMA_THREAD) tc_fence_after();
+        }
+    }
+}
+
+}  // namespace tc

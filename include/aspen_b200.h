@@ -1,0 +1,203 @@
+/*
+ * aspen_b200 -- C ABI of the B200 (sm_100a) execution backend for the ASPEN tile-dataflow runtime.
+ *
+ * Every entry point below replaces the reference function of the same name; a program written
+ * against the reference's public header compiles and links against libaspen_b200.so unchanged
+ * (include/aspen.h in this tree forwards here).  "ref:" gives the reference declaration and the
+ * definition each one stands in for.  Enum VALUES are part of the ABI: they are written as
+ * integers into .aspen files (ref: src/apu_file_io.c:451-452) and passed in `order` arrays.
+ *
+ * All handles are opaque.  Pointer-returning calls give NULL and print to stderr on failure,
+ * void calls print and return (ref: include/aspen.h:36, ERROR_PRTF); the last message is also
+ * kept for aspen_b200_last_error().  Calls are made from one host thread per dse_group.
+ */
+#ifndef ASPEN_B200_H_
+#define ASPEN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+#include <sys/types.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ref: include/aspen.h:26-32 -- graph-geometry constants of the reference tiler */
+#define MAX_TENSOR_DIMS 8
+#define MAX_STRING_LEN 256
+#define MAX_PARENT_NINST_NUM (1 << 16)
+#define NINST_H_MIN 64
+#define NINST_W_MIN 12
+#define MEM_ALIGN 32
+
+/* ref: include/aspen.h:50-65 */
+typedef enum { NINST_NOT_READY, NINST_READY, NINST_COMPLETED, NUM_NINST_STATES } NINST_STATE;
+typedef enum {
+    NO_LAYER_TYPE, INPUT_LAYER, CONV_LAYER, FC_LAYER, RESIDUAL_LAYER, BATCHNORM_LAYER, YOLO_LAYER,
+    APPEND_LAYER, ACTIVATION_LAYER, MAXPOOL_LAYER, AVGPOOL_LAYER, ROUTE_LAYER, SOFTMAX_LAYER,
+    MATMUL_LAYER, LAYERNORM_LAYER, K_ATTENTION_LAYER, V_ATTENTION_LAYER, NUM_LAYER_ELEMENTS
+} LAYER_TYPE;
+typedef enum {
+    OUT_W, OUT_H, OUT_C, BATCH, IN_W, IN_H, IN_C, WEIGHT_W, WEIGHT_H, SUB_C, STRIDE, PADDING,
+    DILATION, GROUPS, NUM_HIDDEN, NUM_HEAD, NUM_SEQ, MAT_M, MAT_N, MAT_K, SUB_M, MASKED,
+    FORM_BYTES, NUM_PARAM_ELEMENTS
+} LAYER_PARAMS;
+typedef enum {
+    NULL_TENSOR, OUTPUT_TENSOR, INPUT_TENSOR, WEIGHT_TENSOR, BIAS_TENSOR, COL_IDX_TENSOR,
+    ANCHOR_TENSOR, BN_VAR_TENSOR, BN_MEAN_TENSOR, BN_WEIGHT_TENSOR, NUM_TENSORS
+} LAYER_TENSORS;
+typedef enum { PARENT_NONE, PARENT_0, PARENT_1, PARENT_WEIGHT, NUM_PARENT_ELEMENTS } LAYER_PARENTS;
+typedef enum {
+    NO_ACTIVATION, SIGMOID, LINEAR, TANH, RELU, LEAKY_RELU, ELU, SELU, GELU, GELU_ACCURATE,
+    NUM_ACTIVATIONS
+} LAYER_ACT;
+typedef enum { RPOOL_DNN, RPOOL_LAYER_TYPE, RPOOL_LAYER_IDX, RPOOL_NASM, RPOOL_DSE, NUM_RPOOL_CONDS } RPOOL_CONDS;
+
+/* ref: include/aspen.h:67-73, src/util.c:3-41 */
+extern char *ninst_state_str[NUM_NINST_STATES];
+extern char *layer_type_str[NUM_LAYER_ELEMENTS];
+extern char *param_type_str[NUM_PARAM_ELEMENTS];
+extern char *tensor_type_str[NUM_TENSORS];
+extern char *parent_type_str[NUM_PARENT_ELEMENTS];
+extern char *activation_type_str[NUM_ACTIVATIONS];
+extern char *rpool_cond_str[NUM_RPOOL_CONDS];
+
+/* ref: include/aspen.h:75-88 */
+typedef struct aspen_dnn_t aspen_dnn_t;
+typedef struct aspen_layer_t aspen_layer_t;
+typedef struct aspen_tensor_t aspen_tensor_t;
+typedef struct ninst_t ninst_t;
+typedef struct nasm_t nasm_t;
+typedef struct nasm_ldata_t nasm_ldata_t;
+typedef struct rpool_t rpool_t;
+typedef struct rpool_queue_t rpool_queue_t;
+typedef struct rpool_queue_group_t rpool_queue_group_t;
+typedef struct dse_t dse_t;
+typedef struct dse_group_t dse_group_t;
+
+/* ---- model: cfg + weights -> layer list ------------------------------------------------- */
+/* ref: include/aspen.h:90, src/apu.c:6-43.  data_path may be NULL (random +-0.3 weights). */
+aspen_dnn_t *apu_create_dnn(char *input_path, char *data_path);
+/* ref: include/aspen.h:91, src/apu.c:45-57.  Refused while a nasm still references the dnn. */
+void apu_destroy_dnn(aspen_dnn_t *dnn);
+/* ref: include/aspen.h:92-93, src/apu_file_io.c:434-809 */
+void apu_save_dnn_to_file(aspen_dnn_t *dnn, char *filename);
+aspen_dnn_t *apu_load_dnn_from_file(char *filename);
+
+/* ---- tile graph ------------------------------------------------------------------------- */
+/* ref: include/aspen.h:95-96, src/apu_nasm.c:601-679.  Tile-count search with the executor in the loop. */
+nasm_t *apu_generate_nasm(aspen_dnn_t *dnn, unsigned int batch_size, unsigned int num_iter);
+nasm_t *apu_generate_transformer_nasm(aspen_dnn_t *dnn, unsigned int batch_size, unsigned int seq_num, unsigned int num_iter);
+/* ref: include/aspen.h:97-98, src/apu_nasm.c:682-751 */
+nasm_t *apu_create_nasm(aspen_dnn_t *dnn, unsigned int min_ninst_per_ldata, unsigned int batch_size);
+nasm_t *apu_create_transformer_nasm(aspen_dnn_t *dnn, unsigned int min_ninst_per_ldata, unsigned int batch_size, unsigned int seq_num);
+/* ref: include/aspen.h:99, src/apu_nasm.c:936-948 */
+void apu_destroy_nasm(nasm_t *nasm);
+/* ref: include/aspen.h:100-101, src/apu_file_io.c:811-1094 */
+nasm_t *apu_load_nasm_from_file(char *filename, aspen_dnn_t *dnn);
+void apu_save_nasm_to_file(nasm_t *nasm, char *filename);
+/* ref: include/aspen.h:102, src/apu_nasm.c:753-771 */
+void apu_reset_nasm(nasm_t *nasm);
+
+/* ---- ready pool ------------------------------------------------------------------------- */
+/* ref: include/aspen.h:104-105, src/rpool.c:47-72 */
+rpool_t *rpool_init(void);
+void rpool_destroy(rpool_t *rpool);
+/* ref: include/aspen.h:106, src/rpool.c:167-193 + src/dse.c:443-470.  input_data: packed NHWC
+ * ([B][H][W][C]) or [B][S][M] fp32 in HOST memory; it is copied, the caller keeps its buffer. */
+void rpool_add_nasm_raw_input(rpool_t *rpool, nasm_t *nasm, void *input_data);
+/* ref: include/aspen.h:107, src/rpool.c:195-223.  File holds NCHW fp32; NULL means zeros. */
+void rpool_add_nasm(rpool_t *rpool, nasm_t *nasm, char *input_filename);
+/* ref: include/aspen.h:108-109, src/rpool.c:262-277 */
+void rpool_reset_queue(rpool_t *rpool);
+void rpool_reset_nasm(rpool_t *rpool, nasm_t *nasm);
+
+/* ---- scheduling engines ----------------------------------------------------------------- */
+/* ref: include/aspen.h:111-113, src/dse.c:110-151.  Here a "dse" is a persistent worker CTA. */
+dse_group_t *dse_group_init(unsigned int num_dse);
+void dse_group_set_rpool(dse_group_t *dse_group, rpool_t *rpool);
+void dse_group_destroy(dse_group_t *dse_group);
+/* ref: include/aspen.h:114-116, src/dse.c:234-277.  run is asynchronous, stop is cooperative. */
+void dse_group_run(dse_group_t *dse_group);
+void dse_group_stop(dse_group_t *dse_group);
+void dse_group_run_until_nasm_completion(dse_group_t *dse_group, nasm_t *nasm);
+/* ref: include/aspen.h:117-118, src/dse.c:260-289 */
+void dse_wait_for_nasm_completion(nasm_t *nasm);
+unsigned int dse_check_nasm_completion(nasm_t *nasm);
+/* ref: include/aspen.h:119-120, src/dse.c:472-518 + src/apu.c:227-297.  *out_ptr is malloc'd
+ * host memory the caller frees; return value is its size in bytes, -1 on bad arguments. */
+ssize_t dse_get_ldata_result(nasm_t *nasm, unsigned int ldata_idx, LAYER_PARAMS *order, void **out_ptr);
+ssize_t dse_get_nasm_result(nasm_t *nasm, LAYER_PARAMS *order, void **out_ptr);
+
+/* ref: include/aspen.h:122, src/util.c:175-192.  Releases the cached activation arenas. */
+void aspen_flush_dynamic_memory(void);
+
+/* ref: include/aspen.h:124-133 */
+void print_aspen_build_info(void);
+void print_dnn_info(aspen_dnn_t *dnn, int print_data);
+void print_layer_info(aspen_layer_t *layer, int print_data);
+void print_tensor_info(aspen_tensor_t *tensor, int print_data);
+void print_nasm_info(nasm_t *nasm, int print_ninst, int print_data);
+void print_ldata_info(nasm_ldata_t *ldata, int print_ninst, int print_data);
+void print_ninst_info(ninst_t *ninst, int print_data);
+void print_rpool_queue_info(rpool_queue_t *rpool_queue);
+void print_rpool_queue_group_info(rpool_queue_group_t *rpool_queue_group);
+void print_rpool_info(rpool_t *rpool);
+
+/* ---- additions of this backend (no counterpart in the reference) ------------------------ */
+
+/* Last error text of the calling process ("" if none). */
+const char *aspen_b200_last_error(void);
+
+/* Engine status of the most recent run of a dse group: 0 ok, otherwise an ASPEN_B200_ERR_* code
+ * written by the device scheduler when a bounded wait ran out (the kernel then returns instead
+ * of spinning). */
+#define ASPEN_B200_OK 0
+#define ASPEN_B200_ERR_STALL 1      /* ready-queue wait ran out: graph cannot make progress   */
+#define ASPEN_B200_ERR_PIPE 2       /* an in-kernel pipeline barrier wait ran out             */
+#define ASPEN_B200_ERR_CUDA 3       /* a CUDA runtime call failed (see aspen_b200_last_error)  */
+int aspen_b200_group_status(dse_group_t *dse_group);
+
+/* Tiler profile.  The reference's constants (64-row / 12-column quanta, 1e8 flop per tile) shape
+ * tiles for an 8x12 AVX2 register block; profile 1 uses 64-row / 128-column quanta so a tile is
+ * whole 128-row tensor-core blocks.  Tile VALUES do not depend on the profile.  Affects nasms
+ * created afterwards.  0 = reference geometry (default), 1 = B200 geometry. */
+void aspen_b200_set_tile_profile(int profile);
+void aspen_b200_set_tile_quanta(unsigned int h_min, unsigned int w_min, unsigned int flop_per_ninst);
+
+/* Arithmetic of the contraction tiles for dse groups created afterwards:
+ * 0 = TF32 operands on tcgen05 tensor cores, fp32 accumulate (default);
+ * 1 = fp32 FFMA validation mode. */
+void aspen_b200_set_precision(int mode);
+
+/* CUDA device used by objects created afterwards on the calling thread (default: current). */
+int aspen_b200_set_device(int device);
+
+/* Read-only views used by the parity tests and the benchmark. */
+unsigned int aspen_b200_dnn_num_layers(aspen_dnn_t *dnn);
+void aspen_b200_dnn_layer_params(aspen_dnn_t *dnn, unsigned int layer_idx, unsigned int *params_out /*[NUM_PARAM_ELEMENTS]*/);
+int aspen_b200_dnn_layer_type(aspen_dnn_t *dnn, unsigned int layer_idx);
+unsigned int aspen_b200_nasm_num_ldata(nasm_t *nasm);
+unsigned int aspen_b200_nasm_num_ninst(nasm_t *nasm);
+uint64_t aspen_b200_nasm_total_flops(nasm_t *nasm);
+/* out[12]: type, activation, H, W, stride, tile H, tile W, num_ninst, flop_per_output, parent0, parent1, mem bytes */
+void aspen_b200_nasm_ldata_info(nasm_t *nasm, unsigned int ldata_idx, unsigned int *out);
+/* out[7]: pos H, pos W, tile H, tile W, num parents, num children, num_input_pos */
+void aspen_b200_nasm_ninst_info(nasm_t *nasm, unsigned int ninst_idx, unsigned int *out);
+/* Copies up to `cap` parent (children) ninst indices; returns the full count. */
+unsigned int aspen_b200_nasm_ninst_parents(nasm_t *nasm, unsigned int ninst_idx, unsigned int *out, unsigned int cap);
+unsigned int aspen_b200_nasm_ninst_children(nasm_t *nasm, unsigned int ninst_idx, unsigned int *out, unsigned int cap);
+/* Packed column-major copy (H contiguous x W columns) of one layer's activations after a run;
+ * returns element count or -1. */
+long aspen_b200_nasm_get_ldata_packed(nasm_t *nasm, unsigned int ldata_idx, float *out);
+
+/* Timed execution for benchmarks: runs the group's rpool `iters` times (re-arming every nasm in
+ * it between runs, as rpool_reset_nasm does) and returns the device time of the runs in
+ * milliseconds measured with CUDA events on the group's stream; *launches_out (may be NULL) gets
+ * the number of kernel launches issued.  Returns a negative value on error. */
+double aspen_b200_group_time_runs(dse_group_t *dse_group, unsigned int warmup, unsigned int iters, unsigned long long *launches_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASPEN_B200_H_ */
