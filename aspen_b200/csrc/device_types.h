@@ -23,6 +23,7 @@ struct LayerDev {
     const float *anchors;
     int wmap;                 // index of the weight tensor map, -1 if none
     unsigned a_vec4;          // activation rows can be fetched in 16-byte pieces (IC % 4 == 0 ...)
+    unsigned round_out;       // store outputs rounded to TF32 (nearest): a tensor-core layer reads them
 };
 
 struct TileDev {
@@ -60,8 +61,7 @@ struct CtrlDev {
     unsigned stop;           // host request: leave after the current tile
     unsigned n_nasm;
     unsigned long long stall_ns;   // no-progress window after which a wait gives up
-    unsigned pipe_spins;           // spin budget of in-kernel pipeline waits
-    unsigned pad_;
+    unsigned long long pipe_ns;    // time budget of in-kernel pipeline waits
 };
 
 struct StatusHost {          // mapped host memory

@@ -142,7 +142,7 @@ struct Engine {
     std::vector<nasm_t *> uploaded;   // graphs whose images (in this order) are in nasms_d
     bool running = false;
     unsigned long long stall_ns = 2000000000ull;
-    unsigned pipe_spins = 200000000u;
+    unsigned long long pipe_ns = 1000000000ull;
     unsigned long long launches = 0;
     float *xfer = nullptr;            // device staging for packed inputs / results
     size_t xfer_bytes = 0;
@@ -162,6 +162,7 @@ struct DeviceNasm {
     void *wmaps = nullptr;
     NasmDev host;        // template; tile_base / queue_base are filled per run
     bool armed = false;  // has input, counters will be reset at the next run
+    bool round_input = false;   // tensor-core path: the input is rounded to TF32 after upload
     bool ran = false;
 };
 
@@ -211,7 +212,7 @@ Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) 
     e->n_ctas = (unsigned)e->num_sms;
     if (env_u64("ASPEN_B200_CTAS", &v) && v > 0 && v <= (unsigned long long)e->num_sms) e->n_ctas = (unsigned)v;
     if (env_u64("ASPEN_B200_STALL_MS", &v) && v > 0) e->stall_ns = v * 1000000ull;
-    if (env_u64("ASPEN_B200_PIPE_SPINS", &v) && v > 0) e->pipe_spins = (unsigned)std::min<unsigned long long>(v, 0xffffffffull);
+    if (env_u64("ASPEN_B200_PIPE_MS", &v) && v > 0) e->pipe_ns = v * 1000000ull;
     e->smem_bytes = (precision == 0 ? (size_t)tc::STAGES * tc::STAGE_BYTES : 0) + sizeof(tc::Shared) + 1024;
     bool ok = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking) == cudaSuccess &&
@@ -275,6 +276,9 @@ __global__ void unpack_columns(float *dst, const float *src, unsigned H, unsigne
         unsigned h = (unsigned)(i - w * H);
         dst[w * ld + h] = src[i];
     }
+}
+__global__ void round_tf32_inplace(float *p, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) p[i] = tf32_round(p[i]);
 }
 __global__ void pack_columns(float *dst, const float *src, unsigned H, unsigned ld, size_t n) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -376,6 +380,17 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
             }
         }
     }
+    if (e->precision == 0) {
+        for (unsigned i = 0; i < nasm->num_ldata; i++) {
+            const LAYER_TYPE t = nasm->ldata[i].layer->type;
+            if (t == CONV_LAYER || t == FC_LAYER || t == MATMUL_LAYER || t == K_ATTENTION_LAYER || t == V_ATTENTION_LAYER)
+                for (int k = PARENT_0; k <= PARENT_1; k++) {
+                    unsigned par = nasm->ldata[i].parent_ldata_idx_arr[k];
+                    if (par != (unsigned)-1) layers[par].round_out = 1;
+                }
+        }
+    }
+    dn->round_input = layers[0].round_out != 0;
     if (to_device(&dn->layers, layers) != 0) return -1;
     {
         size_t bytes = std::max<size_t>(maps.size(), 1) * sizeof(CUtensorMap);
@@ -453,6 +468,11 @@ int engine_set_input(nasm_t *nasm, const void *input_host) {
         unpack_columns<<<blocks, 256, 0, e->stream>>>(dst, e->xfer, l0.out_mat_dims[OUT_H], l0.out_mat_stride, n);
         e->launches++;
         CUDA_TRY(cudaGetLastError());
+    }
+    if (dn->round_input) {
+        size_t total = l0.out_mat_mem_size / sizeof(float);
+        round_tf32_inplace<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, e->stream>>>(dst, total);
+        e->launches++;
     }
     // The caller may reuse its buffer as soon as we return (the reference copies synchronously).
     CUDA_TRY(cudaStreamSynchronize(e->stream));
@@ -534,7 +554,7 @@ static int launch_run(Engine *e, const std::vector<nasm_t *> &run) {
     e->status_h->status = 0;
     e->status_h->tiles_done = 0;
     unsigned arm_blocks = std::min<unsigned>((total + 255) / 256, 1024);
-    sched::arm_kernel<<<arm_blocks, 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue, total, n_init, n_input, e->stall_ns, e->pipe_spins);
+    sched::arm_kernel<<<arm_blocks, 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue, total, n_init, n_input, e->stall_ns, e->pipe_ns);
     sched::seed_kernel<<<std::max(1u, std::min<unsigned>((n_init + 255) / 256, 256)), 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue);
     if (e->precision == 0)
         sched::scheduler_kernel<true><<<e->n_ctas, tc::NTHREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d);

@@ -131,7 +131,7 @@ __device__ unsigned complete_tile(const NasmDev &G, unsigned local, CtrlDev *ctr
 // Resets the counters of every graph in the run and seeds the queue with the tiles that only
 // depend on input tiles (push_first_layer_to_rpool, ref src/dse.c:443-470).
 __global__ void arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, unsigned total, unsigned n_init_total,
-                           unsigned n_input_total, unsigned long long stall_ns, unsigned pipe_spins) {
+                           unsigned n_input_total, unsigned long long stall_ns, unsigned long long pipe_ns) {
     const unsigned stride = gridDim.x * blockDim.x, t0 = blockIdx.x * blockDim.x + threadIdx.x;
     const unsigned n_nasm = ctrl->n_nasm;
     for (unsigned i = t0; i < total; i += stride) queue[i] = 0u;
@@ -144,7 +144,7 @@ __global__ void arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, unsig
     }
     if (t0 == 0) {
         ctrl->head = 0u; ctrl->tail = n_init_total; ctrl->done = n_input_total; ctrl->total = total; ctrl->cap = total;
-        ctrl->abort = 0u; ctrl->stop = 0u; ctrl->stall_ns = stall_ns; ctrl->pipe_spins = pipe_spins;
+        ctrl->abort = 0u; ctrl->stop = 0u; ctrl->stall_ns = stall_ns; ctrl->pipe_ns = pipe_ns;
     }
 }
 // Second step of arming (after every slot was cleared): write the initial ready tiles.

@@ -29,6 +29,18 @@ __device__ __forceinline__ float activate(float x, int act) {
     }
 }
 
+// The tensor cores read only the upper 19 bits of an fp32 operand (TF32), i.e. they truncate.
+// Truncation is biased toward zero and the bias compounds over a deep network, so every layer whose
+// output feeds a tensor-core layer stores values already rounded to nearest TF32; the later
+// truncation is then exact.  (Weights are rounded the same way when they are uploaded.)
+__device__ __forceinline__ float tf32_round(float x) {
+    unsigned u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
+__device__ __forceinline__ float finish(float x, const LayerDev &L) { x = activate(x, L.act); return L.round_out ? tf32_round(x) : x; }
+__device__ __forceinline__ float store_round(float x, const LayerDev &L) { return L.round_out ? tf32_round(x) : x; }
+
 // Output pixel (flattened column index) -> batch and top-left input coordinate of its window.
 struct PixelWin { int b, ih0, iw0; };
 __device__ __forceinline__ PixelWin pixel_window(const LayerDev &L, unsigned col) {
@@ -57,11 +69,11 @@ __device__ void tile_residual(const LayerDev &L, const TileDev &T, unsigned tid,
         if (j < h4) {
             unsigned m = T.pos_h + 4 * j;
             float4 a = ldcg4(L.in0 + col * L.ld0 + m), b = ldcg4(L.in1 + col * L.ld1 + m);
-            float4 o = {activate(a.x + b.x, L.act), activate(a.y + b.y, L.act), activate(a.z + b.z, L.act), activate(a.w + b.w, L.act)};
+            float4 o = {finish(a.x + b.x, L), finish(a.y + b.y, L), finish(a.z + b.z, L), finish(a.w + b.w, L)};
             *reinterpret_cast<float4 *>(L.out + col * L.ldc + m) = o;
         } else {
             unsigned m = T.pos_h + 4 * h4 + (j - h4);
-            L.out[col * L.ldc + m] = activate(ldcg1(L.in0 + col * L.ld0 + m) + ldcg1(L.in1 + col * L.ld1 + m), L.act);
+            L.out[col * L.ldc + m] = finish(ldcg1(L.in0 + col * L.ld0 + m) + ldcg1(L.in1 + col * L.ld1 + m), L);
         }
     }
 }
@@ -92,10 +104,10 @@ __device__ void tile_pool(const LayerDev &L, const TileDev &T, unsigned tid, uns
             }
         if (!IS_MAX) { acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv; }
         if (vec) {
-            float4 o = {activate(acc.x, L.act), activate(acc.y, L.act), activate(acc.z, L.act), activate(acc.w, L.act)};
+            float4 o = {finish(acc.x, L), finish(acc.y, L), finish(acc.z, L), finish(acc.w, L)};
             *reinterpret_cast<float4 *>(L.out + col * L.ldc + m) = o;
         } else {
-            L.out[col * L.ldc + m] = activate(acc.x, L.act);
+            L.out[col * L.ldc + m] = finish(acc.x, L);
         }
     }
 }
@@ -136,12 +148,13 @@ __device__ void tile_layernorm(const LayerDev &L, const TileDev &T, unsigned tid
             float4 g = *reinterpret_cast<const float4 *>(gain + m);
             float4 o = {(v.x - mean) * inv * g.x, (v.y - mean) * inv * g.y, (v.z - mean) * inv * g.z, (v.w - mean) * inv * g.w};
             if (shift) { float4 b = *reinterpret_cast<const float4 *>(shift + m); o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w; }
+            o.x = store_round(o.x, L); o.y = store_round(o.y, L); o.z = store_round(o.z, L); o.w = store_round(o.w, L);
             *reinterpret_cast<float4 *>(y + m) = o;
         }
         for (unsigned m = M4 + lane; m < M; m += 32) {
             float o = (ldcg1(x + m) - mean) * inv * gain[m];
             if (shift) o += shift[m];
-            y[m] = o;
+            y[m] = store_round(o, L);
         }
     }
 }
@@ -159,7 +172,7 @@ __device__ void tile_softmax(const LayerDev &L, const TileDev &T, unsigned tid, 
         float s = 0.f;
         for (unsigned m = lane; m < M; m += 32) s += expf(ldcg1(x + m) - mx);
         s = warp_sum(s);
-        for (unsigned m = lane; m < M; m += 32) y[m] = expf(ldcg1(x + m) - mx) / s;
+        for (unsigned m = lane; m < M; m += 32) y[m] = store_round(expf(ldcg1(x + m) - mx) / s, L);
     }
 }
 
@@ -182,7 +195,7 @@ __device__ void tile_yolo(const LayerDev &L, const TileDev &T, unsigned tid, uns
         else if (j == 2) o = expf(v) * L.anchors[2 * aidx];
         else if (j == 3) o = expf(v) * L.anchors[2 * aidx + 1];
         else o = 1.0f / (1.0f + expf(-v));
-        out[j] = o;
+        out[j] = store_round(o, L);
     }
 }
 
@@ -197,7 +210,7 @@ __device__ void tile_append(const LayerDev &L, const TileDev &T, unsigned tid, u
         unsigned widx1 = widx2 / s, hidx1 = hidx2 / s;
         float v = c < c1 ? ldcg1(L.in0 + (size_t)(hidx1 * w1 + widx1) * L.ld0 + c)
                          : ldcg1(L.in1 + (size_t)(hidx2 * w2 + widx2) * L.ld1 + (c - c1));
-        L.out[(size_t)w_pos * L.ldc + c] = v;
+        L.out[(size_t)w_pos * L.ldc + c] = store_round(v, L);
     }
 }
 

@@ -71,12 +71,20 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned 
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false (and marks the run aborted) when the budget runs out.
+// Bounded wait.  Returns false (and marks the run aborted) when the time budget runs out.
 __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned parity, CtrlDev *ctrl, StatusHost *status, unsigned where) {
-    const unsigned budget = ctrl->pipe_spins;
-    for (unsigned spin = 0; spin < budget; spin++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    const unsigned long long budget = ctrl->pipe_ns;
+    for (unsigned spin = 1;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 1023u) == 1023u && *(volatile unsigned *)&ctrl->abort) return false;
+        if ((spin & 255u) == 0u) {
+            if (*(volatile unsigned *)&ctrl->abort) return false;
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (now - t0 > budget) break;
+        }
     }
     if (atomicCAS(&ctrl->abort, 0u, (unsigned)ASPEN_B200_ERR_PIPE) == 0u) {
         status->info0 = where;
@@ -352,7 +360,7 @@ __device__ void tile_gemm(const LayerDev &L, const TileDev &T, const NasmDev &G,
                         for (unsigned j = 0; j < 32; j++) {
                             const unsigned m = ms + c * 32u + j;
                             float x = (L.masked && (T.pos_h + m) > q) ? -1e10f : v[j];
-                            v[j] = expf(x / scale) / sum;
+                            v[j] = store_round(expf(x / scale) / sum, L);
                         }
                         if (row_ok && !ps.dead) {
                             #pragma unroll
@@ -371,8 +379,11 @@ __device__ void tile_gemm(const LayerDev &L, const TileDev &T, const NasmDev &G,
                             for (unsigned j = 0; j < 32; j++) {
                                 float x = v[j];
                                 if (bias && j < valid) x += __ldg(bias + c * 32u + j);
-                                v[j] = activate(x, L.act);
+                                v[j] = finish(x, L);
                             }
+                        } else {
+                            #pragma unroll
+                            for (unsigned j = 0; j < 32; j++) v[j] = store_round(v[j], L);
                         }
                         if (row_ok && !ps.dead) {
                             if (valid == 32u) {
