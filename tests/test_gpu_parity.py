@@ -1,0 +1,247 @@
+"""Parity of the device engine (through the C ABI) with the CPU oracle, layer by layer.
+
+Oracle: the unmodified reference's own tile kernels walked layer by layer (oracle/_ref, built from
+the reference sources) when that build is present, else the plain-C restatement (oracle/port.py).
+
+Tolerances (written here once):
+  fp32 FFMA mode  : an element differs when rel >= 1e-4 AND abs >= 1e-5 * max|layer|  -> none may differ
+                    (the mismatch rule of the reference's compare_float_array, src/util.c:368-391)
+  TF32 tensor-core mode : max|got - want| <= 1e-2 * max|want| for every layer (logits and every hidden
+                    state), and the top-1 class of every sample is identical for classifier networks.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+import harness
+from aspen_b200 import api, cfgs, weights
+from oracle import port, ref
+
+pytestmark = pytest.mark.gpu
+
+FP32_REL, FP32_ABS = 1e-4, 1e-5
+TF32_NORM = 1e-2
+CLASSIFIERS = {"tiny_cnn", "custom", "resnet50", "vgg16"}
+
+
+def oracle_layers(name, cfg, wf, batch, seq, min_ninst, x):
+    if ref.available():
+        rn = ref.RefNet(cfg, wf, batch, seq, min_ninst=min_ninst)
+        rn.walk(x)
+        outs = [None] + [rn.ldata(i) for i in range(1, rn.num_ldata)]
+        rn.close()
+        return outs
+    kw, scheme, (wseed, _) = harness.NETS[name]
+    text, wl = cfgs.BUILDERS[harness._BUILDER.get(name, name)](**kw)
+    return port.run(text, weights.make_weights(wl, wseed, scheme), x, batch, seq)
+
+
+def check_layers(dev, outs, precision, name):
+    worst = 0.0
+    for i in range(1, dev.nasm.num_ldata):
+        got, want = dev.nasm.ldata(i), outs[i]
+        assert got.shape == want.shape
+        scale = float(np.abs(want).max())
+        if precision == 1:
+            bad, ea, er = harness.compare(got, want, FP32_REL, FP32_ABS * scale)
+            assert bad == 0, f"{name} layer {i}: {bad} mismatches (max abs {ea:.3e}, max rel {er:.3e})"
+        else:
+            err = float(np.abs(got.astype(np.float64) - want).max()) / max(scale, 1e-30)
+            worst = max(worst, err)
+            assert err <= TF32_NORM, f"{name} layer {i}: normalised error {err:.3e}"
+    if name in CLASSIFIERS:
+        last = dev.nasm.num_ldata - 1
+        assert (dev.nasm.ldata(last).argmax(1) == outs[last].argmax(1)).all()
+    return worst
+
+
+CASES = [
+    # net, batch, seq, min_ninst, precision (0 tf32 / 1 fp32), tile profile (0 reference / 1 b200)
+    ("tiny_cnn", 2, 0, 20, 1, 0), ("tiny_cnn", 2, 0, 20, 0, 0), ("tiny_cnn", 5, 0, 3, 0, 1),
+    ("tiny_transformer", 2, 16, 20, 1, 0), ("tiny_transformer", 2, 16, 20, 0, 0), ("tiny_transformer", 3, 40, 5, 0, 1),
+    ("tiny_gpt", 2, 16, 20, 1, 0), ("tiny_gpt", 2, 16, 20, 0, 0), ("tiny_gpt", 1, 100, 7, 0, 1), ("tiny_gpt", 1, 100, 7, 1, 1),
+    ("custom", 2, 0, 50, 1, 0), ("custom", 7, 0, 50, 0, 1),
+    ("resnet50", 1, 0, 50, 1, 0), ("resnet50", 4, 0, 100, 0, 0), ("resnet50", 4, 0, 100, 0, 1),
+    ("bert_base", 1, 128, 20, 1, 0), ("bert_base", 4, 128, 100, 0, 0), ("bert_base", 4, 128, 100, 0, 1),
+    ("gpt2_124M", 2, 64, 50, 0, 0), ("gpt2_124M", 1, 512, 100, 0, 1),
+    ("vgg16", 1, 0, 100, 0, 1),
+]
+
+
+@pytest.mark.parametrize("name,batch,seq,mn,precision,profile", CASES)
+def test_every_layer_matches_oracle(name, batch, seq, mn, precision, profile, workdir):
+    if not ref.available() and name in ("resnet50", "bert_base", "gpt2_124M", "vgg16"):
+        pytest.skip("plain-C oracle is too slow for this size; needs the reference build")
+    cfg, wf = harness.prepare(name, workdir)
+    dev = harness.Device(cfg, wf, batch, seq, mn, precision, profile)
+    x = harness.make_input(name, dev.input_shape())
+    assert dev.run(x) == 0, api.last_error()
+    outs = oracle_layers(name, cfg, wf, batch, seq, mn, x)
+    check_layers(dev, outs, precision, name)
+    dev.close()
+
+
+@pytest.mark.skipif(not ref.available(), reason="needs the reference build")
+@pytest.mark.parametrize("name,batch,seq", [("resnet50", 32, 0), ("bert_base", 32, 128)])
+def test_benchmark_configuration_matches_oracle(name, batch, seq, workdir):
+    """The benchmark's own workload (batch 32, B200 tile profile, TF32) against the reference."""
+    cfg, wf = harness.prepare(name, workdir)
+    dev = harness.Device(cfg, wf, batch, seq, 296, 0, 1)
+    x = harness.make_input(name, dev.input_shape())
+    assert dev.run(x) == 0, api.last_error()
+    outs = oracle_layers(name, cfg, wf, batch, seq, 296, x)
+    worst = check_layers(dev, outs, 0, name)
+    assert worst < TF32_NORM
+    dev.close()
+
+
+def test_rerun_is_bitwise_identical_and_batch_samples_are_independent(workdir):
+    cfg, wf = harness.prepare("resnet50", workdir)
+    dev = harness.Device(cfg, wf, 4, 0, 100, 0, 1)
+    x = harness.make_input("resnet50", dev.input_shape())
+    assert dev.run(x) == 0
+    last = dev.nasm.num_ldata - 1
+    first = dev.nasm.ldata(last).copy()
+    mid = dev.nasm.ldata(40).copy()
+    assert dev.rerun() == 0                    # rpool_reset_nasm keeps the input resident in layer 0
+    assert np.array_equal(first, dev.nasm.ldata(last)) and np.array_equal(mid, dev.nasm.ldata(40))
+    dev.close()
+    # sample 2 alone gives the same logits as sample 2 inside the batch (tiles never mix samples)
+    one = harness.Device(cfg, wf, 1, 0, 50, 0, 0)
+    per = x.shape[0] // 4
+    assert one.run(x[2 * per:3 * per]) == 0
+    np.testing.assert_array_equal(one.nasm.ldata(last)[0], first[2])
+    one.close()
+
+
+def test_result_api_orders(workdir):
+    cfg, wf = harness.prepare("tiny_cnn", workdir)
+    dev = harness.Device(cfg, wf, 3, 0, 4, 1, 0)
+    x = harness.make_input("tiny_cnn", dev.input_shape())
+    assert dev.run(x) == 0
+    # layer 7 is a conv output: native [B][H][W][C]; ask for NCHW like the reference's main.c:131
+    native = dev.nasm.ldata(7)
+    info = dev.nasm.ldata_info(7)
+    arr = (C.c_int * 4)(api.BATCH, api.OUT_C, api.OUT_H, api.OUT_W)
+    ptr = C.c_void_p()
+    n = api.lib().dse_get_ldata_result(dev.nasm.h, 7, arr, C.byref(ptr))
+    assert n == native.size * 4
+    got = np.frombuffer(C.string_at(ptr, n), np.float32).reshape(3, info["H"], 5, 5)
+    api.lib()._free(ptr)
+    np.testing.assert_array_equal(got, native.reshape(3, 5, 5, info["H"]).transpose(0, 3, 1, 2))
+    # final softmax layer: [B][C]
+    res = dev.nasm.result([api.BATCH, api.OUT_C, api.OUT_H, api.OUT_W])
+    np.testing.assert_array_equal(res.reshape(3, 10), dev.nasm.ldata(dev.nasm.num_ldata - 1))
+    np.testing.assert_allclose(res.reshape(3, 10).sum(1), 1.0, rtol=1e-5)
+    dev.close()
+
+
+def test_input_from_nchw_file_and_null_input(workdir):
+    cfg, wf = harness.prepare("tiny_cnn", workdir)
+    dev = harness.Device(cfg, wf, 2, 0, 4, 1, 0)
+    nchw = harness.make_input("tiny_cnn", (2, 3, 20, 20))
+    path = os.path.join(workdir, "in.tensor")
+    nchw.tofile(path)
+    L = api.lib()
+    L.rpool_add_nasm(dev.rpool.h, dev.nasm.h, path.encode())
+    dev.group.run(); dev.group.wait(dev.nasm); dev.group.stop()
+    a = dev.nasm.ldata(dev.nasm.num_ldata - 1).copy()
+    assert dev.run(np.ascontiguousarray(nchw.transpose(0, 2, 3, 1)).reshape(-1, 3)) == 0
+    np.testing.assert_array_equal(a, dev.nasm.ldata(dev.nasm.num_ldata - 1))
+    L.rpool_add_nasm(dev.rpool.h, dev.nasm.h, None)          # NULL file: zeros (ref src/apu.c:646-649)
+    dev.group.run(); dev.group.wait(dev.nasm); dev.group.stop()
+    assert np.all(dev.nasm.ldata(0) == 0)
+    dev.close()
+
+
+def test_co_inference_two_networks_in_one_rpool(workdir):
+    """Several nasms in one rpool interleave in one scheduler run (reference examples/2.
+    batched_execution_example/aspen_execute.c:48-67)."""
+    cfg_a, wf_a = harness.prepare("tiny_cnn", workdir)
+    cfg_b, wf_b = harness.prepare("custom", workdir)
+    L = api.lib()
+    da, db = api.Dnn(cfg_a, wf_a), api.Dnn(cfg_b, wf_b)
+    na, nb, nc = api.Nasm(da, 2, 0, 8), api.Nasm(db, 3, 0, 8), api.Nasm(da, 1, 0, 8)
+    rp, grp = api.Rpool(), api.DseGroup(0, 1)
+    grp.set_rpool(rp)
+    xs = []
+    for name, nasm in (("tiny_cnn", na), ("custom", nb), ("tiny_cnn", nc)):
+        i0 = nasm.ldata_info(0)
+        xs.append(harness.make_input(name, (i0["W"], i0["H"])))
+        rp.add(nasm, xs[-1])
+    grp.run()
+    for nasm in (na, nb, nc):
+        grp.wait(nasm)
+        assert L.dse_check_nasm_completion(nasm.h) == 1
+    grp.stop()
+    assert grp.status() == 0
+    together = [n.ldata(n.num_ldata - 1).copy() for n in (na, nb, nc)]
+    # each alone gives the same bits
+    for idx, (nasm, x) in enumerate(zip((na, nb, nc), xs)):
+        rp2, g2 = api.Rpool(), api.DseGroup(0, 1)
+        g2.set_rpool(rp2)
+        solo = api.Nasm(nasm.dnn, nasm.ldata_info(0)["W"] // (400 if idx != 1 else 1024), 0, 8)
+        rp2.add(solo, x)
+        g2.run(); g2.wait(solo); g2.stop()
+        np.testing.assert_array_equal(solo.ldata(solo.num_ldata - 1), together[idx])
+        g2.close(); solo.close(); rp2.close()
+    grp.close()
+    for n in (na, nb, nc):
+        n.close()
+    rp.close(); da.close(); db.close()
+
+
+def test_unsatisfiable_graph_reports_stall_instead_of_hanging(workdir, monkeypatch):
+    """A tile that lists the same parent twice can never reach its count: the bounded ready-queue
+    wait gives up, the run ends with ASPEN_B200_ERR_STALL and the context stays usable."""
+    monkeypatch.setenv("ASPEN_B200_STALL_MS", "300")
+    cfg, wf = harness.prepare("tiny_cnn", workdir)
+    dnn = api.Dnn(cfg, wf)
+    good = api.Nasm(dnn, 1, 0, 4)
+    path = os.path.join(workdir, "stall.nasm")
+    good.save(path)
+    lines = open(path).read().split("\n")
+    t = sum(good.ldata_info(i)["num_ninst"] for i in range(9))      # first tile of the connected layer
+    k = lines.index(f"\tNINST_IDX:{t}")
+    n_par = int(lines[k + 2].split(":")[1])
+    first_parent = lines[k + 4]
+    lines[k + 2] = f"\tNUM_PARENT_NINSTS:{n_par + 1}"
+    lines.insert(k + 4 + n_par, f"\t\t{n_par} {first_parent.split()[1]}")
+    open(path, "w").write("\n".join(lines))
+    bad = api.Nasm.load(dnn, path)
+    rp, grp = api.Rpool(), api.DseGroup(0, 1)
+    grp.set_rpool(rp)
+    rp.add(bad, None)
+    grp.run()
+    grp.wait(bad)
+    grp.stop()
+    assert grp.status() == 1                                   # ASPEN_B200_ERR_STALL
+    assert api.lib().dse_check_nasm_completion(bad.h) == 0
+    # the same group still runs a healthy graph afterwards
+    rp2 = api.Rpool()
+    grp.close(); bad.close(); rp.close()
+    g2 = api.DseGroup(0, 1)
+    g2.set_rpool(rp2)
+    rp2.add(good, None)
+    g2.run(); g2.wait(good); g2.stop()
+    assert g2.status() == 0 and api.lib().dse_check_nasm_completion(good.h) == 1
+    g2.close(); good.close(); rp2.close(); dnn.close()
+
+
+def test_stop_then_run_again_completes(workdir):
+    cfg, wf = harness.prepare("resnet50", workdir)
+    dev = harness.Device(cfg, wf, 4, 0, 100, 0, 1)
+    x = harness.make_input("resnet50", dev.input_shape())
+    dev.rpool.add(dev.nasm, x)
+    dev.group.run()
+    dev.group.stop()                       # cooperative stop, possibly mid-graph
+    dev.group.run()                        # unfinished graph restarts
+    dev.group.wait(dev.nasm)
+    dev.group.stop()
+    assert dev.group.status() == 0 and api.lib().dse_check_nasm_completion(dev.nasm.h) == 1
+    a = dev.nasm.ldata(dev.nasm.num_ldata - 1).copy()
+    assert dev.rerun() == 0
+    np.testing.assert_array_equal(a, dev.nasm.ldata(dev.nasm.num_ldata - 1))
+    dev.close()

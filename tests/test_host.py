@@ -1,0 +1,220 @@
+"""Host side of the library on CPU: cfg parsing, the tiler and dependency graph against the
+reference's geometry (fixtures and, when present, the reference itself), file codecs, the error
+conventions of the C API, and that the shared library exports every declared entry point."""
+import ctypes as C
+import hashlib
+import json
+import glob
+import os
+import re
+
+import numpy as np
+import pytest
+
+import harness
+from aspen_b200 import api, cfgs
+from oracle import ref
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+REFDIR = "/root/reference"
+
+
+def _digest(path):
+    h = hashlib.sha256()
+    for line in open(path, "rb"):
+        if not line.startswith(b"DNN_NAME"):
+            h.update(line)
+    return h.hexdigest()
+
+
+def test_library_exports_every_declared_symbol():
+    L = api.lib()
+    header = open(os.path.join(ROOT, "include", "aspen_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    names = set(re.findall(r"\b([a-z_0-9]+)\s*\(", header)) - {"defined", "sizeof"}
+    declared = {n for n in names if re.match(r"^(apu_|rpool_|dse_|print_|aspen_)", n)}
+    assert len(declared) >= 55
+    assert declared == set(api.EXPORTS), declared ^ set(api.EXPORTS)
+    for n in declared:
+        assert hasattr(L, n), n
+
+
+GRAPHS = sorted(glob.glob(os.path.join(GOLDEN, "graph_*.json")))
+
+
+@pytest.mark.parametrize("path", GRAPHS, ids=[os.path.basename(p)[6:-5] for p in GRAPHS])
+def test_tiler_and_graph_match_reference_fixture(path, workdir):
+    g = json.load(open(path))
+    if g["net"] in ("vgg16",) and os.environ.get("ASPEN_FAST_TESTS"):
+        pytest.skip("large")
+    cfg = os.path.join(workdir, g["net"] + "_g.cfg")
+    cfgs.write_cfg(harness._BUILDER.get(g["net"], g["net"]), cfg, **harness.NETS[g["net"]][0])
+    dnn = api.Dnn(cfg)
+    nasm = api.Nasm(dnn, g["batch"], g["seq"], g["min_ninst"])
+    assert nasm.num_ninst == g["num_ninst"]
+    for i, row in enumerate(g["ldata"]):
+        info = nasm.ldata_info(i)
+        assert [info[k] for k in api.LDATA_FIELDS] == row, (i, info, row)
+    out = os.path.join(workdir, "mine.nasm")
+    nasm.save(out)
+    assert _digest(out) == g["nasm_sha256"]          # parent order, child order, num_input_pos: all identical
+    # a file written here loads back to the same graph
+    again = api.Nasm.load(dnn, out)
+    for t in (0, nasm.num_ninst // 2, nasm.num_ninst - 1):
+        assert again.parents(t) == nasm.parents(t) and again.children(t) == nasm.children(t)
+    again.close()
+    nasm.close()
+    dnn.close()
+
+
+@pytest.mark.skipif(not os.path.isdir(REFDIR), reason="reference tree not mounted")
+@pytest.mark.parametrize("net,fname", [("resnet50", "resnet50_B2.nasm"), ("resnet50", "resnet50_B4.nasm")])
+def test_shipped_nasm_files_load(net, fname, workdir):
+    cfg = os.path.join(workdir, net + "_s.cfg")
+    cfgs.write_cfg(net, cfg)
+    dnn = api.Dnn(cfg)
+    path = os.path.join(REFDIR, "files", net, fname)
+    nasm = api.Nasm.load(dnn, path)
+    out = os.path.join(workdir, "reload.nasm")
+    nasm.save(out)
+    assert _digest(out) == _digest(path)
+    nasm.close()
+    dnn.close()
+
+
+@pytest.mark.skipif(not os.path.isdir(REFDIR), reason="reference tree not mounted")
+@pytest.mark.parametrize("net", ["resnet50", "vgg16", "bert_base", "gpt2_124M", "custom"])
+def test_generated_cfg_equals_reference_cfg(net, workdir):
+    """The cfg builders stand in for the reference's files/*.cfg on machines without the reference."""
+    mine = os.path.join(workdir, net + "_c.cfg")
+    cfgs.write_cfg(net, mine)
+    theirs = os.path.join(REFDIR, "files", "custom.cfg" if net == "custom" else f"{net}/{net}_aspen.cfg")
+    a, b = api.Dnn(mine), api.Dnn(theirs)
+    assert a.num_layers == b.num_layers
+    for i in range(a.num_layers):
+        assert a.layer_type(i) == b.layer_type(i) and a.layer_params(i) == b.layer_params(i), i
+    a.close()
+    b.close()
+
+
+@pytest.mark.skipif(not ref.available(), reason="reference build (oracle/_ref) not present")
+def test_layer_params_match_reference_parser(workdir):
+    for net in ("tiny_cnn", "tiny_gpt", "resnet50"):
+        cfg, _ = harness.prepare(net, workdir)
+        mine = api.Dnn(cfg)
+        rn = ref.RefNet(cfg, None, 1, 8 if "gpt" in net else 0, min_ninst=1)
+        for i in range(mine.num_layers):
+            assert mine.layer_params(i) == rn.layer_params(i)[:api.NUM_PARAM_ELEMENTS], (net, i)
+        rn.close()
+        mine.close()
+
+
+def test_b200_tile_profile_only_changes_geometry(workdir):
+    cfg, _ = harness.prepare("resnet50", workdir)
+    dnn = api.Dnn(cfg)
+    a = api.Nasm(dnn, 4, 0, 100)
+    api.lib().aspen_b200_set_tile_profile(1)
+    b = api.Nasm(dnn, 4, 0, 100)
+    api.lib().aspen_b200_set_tile_profile(0)
+    assert a.total_flops == b.total_flops == 4 * 8185945088
+    for i in range(a.num_ldata):
+        ia, ib = a.ldata_info(i), b.ldata_info(i)
+        assert (ia["H"], ia["W"]) == (ib["H"], ib["W"])
+        if ib["type"] == 2 and ib["W"] >= 128:        # conv tiles are whole 128-column blocks
+            assert ib["tile_w"] % 128 == 0
+    # every tile has parents, parents precede children
+    for t in range(b.ldata_info(0)["num_ninst"], b.num_ninst, 97):
+        ps = b.parents(t)
+        assert ps and max(ps) < t
+    a.close(); b.close(); dnn.close()
+
+
+def test_weight_file_and_aspen_codec_roundtrip(workdir):
+    cfg, wf = harness.prepare("tiny_cnn", workdir)
+    L = api.lib()
+    dnn = api.Dnn(cfg, wf)
+    path = os.path.join(workdir, "tiny.aspen").encode()
+    L.apu_save_dnn_to_file(dnn.h, path)
+    h2 = L.apu_load_dnn_from_file(path)
+    assert h2
+    assert L.aspen_b200_dnn_num_layers(h2) == dnn.num_layers
+    for i in range(dnn.num_layers):
+        buf = (C.c_uint * api.NUM_PARAM_ELEMENTS)()
+        L.aspen_b200_dnn_layer_params(h2, i, buf)
+        assert list(buf) == dnn.layer_params(i)
+    path2 = os.path.join(workdir, "tiny2.aspen").encode()
+    L.apu_save_dnn_to_file(h2, path2)
+    assert open(path, "rb").read() == open(path2, "rb").read()
+    L.apu_destroy_dnn(h2)
+    dnn.close()
+
+
+@pytest.mark.skipif(not ref.available(), reason="reference build (oracle/_ref) not present")
+def test_aspen_file_is_readable_by_reference(workdir):
+    cfg, wf = harness.prepare("tiny_cnn", workdir)
+    L, R = api.lib(), ref.lib()
+    dnn = api.Dnn(cfg, wf)
+    mine = os.path.join(workdir, "m.aspen").encode()
+    L.apu_save_dnn_to_file(dnn.h, mine)
+    R.apu_load_dnn_from_file.restype = C.c_void_p
+    R.apu_load_dnn_from_file.argtypes = [C.c_char_p]
+    R.apu_save_dnn_to_file.argtypes = [C.c_void_p, C.c_char_p]
+    rd = R.apu_load_dnn_from_file(mine)
+    assert rd
+    theirs = os.path.join(workdir, "t.aspen").encode()
+    R.apu_save_dnn_to_file(rd, theirs)
+    a, b = open(mine, "rb").read(), open(theirs, "rb").read()
+    strip = lambda s: re.sub(rb"ASPEN_BUILD:[^\n]*\n", b"", s)
+    assert strip(a) == strip(b)                      # same tensors, same packed weight layout, byte for byte
+    dnn.close()
+
+
+def test_error_conventions(workdir, capfd):
+    L = api.lib()
+    assert L.apu_create_dnn(b"/nonexistent/x.cfg", None) is None
+    assert "Couldn't open" in api.last_error() or "no sections" in api.last_error()
+    assert L.apu_create_dnn(b"model.txt", None) is None
+    cfg, _ = harness.prepare("tiny_cnn", workdir)
+    dnn = api.Dnn(cfg)
+    assert L.apu_create_nasm(dnn.h, 0, 1) is None          # min_ninst_per_ldata must be >= 1
+    nasm = api.Nasm(dnn, 1, 0, 4)
+    L.apu_destroy_dnn(dnn.h)                                # refused: a nasm still references the dnn
+    assert "still referencing" in api.last_error()
+    assert dnn.num_layers == 11
+    assert L.apu_load_nasm_from_file(b"/nonexistent.nasm", dnn.h) is None
+    ptr = C.c_void_p()
+    assert L.dse_get_nasm_result(None, None, C.byref(ptr)) == -1
+    assert L.dse_get_nasm_result(nasm.h, None, None) == -1
+    rp = L.rpool_init()
+    L.rpool_add_nasm_raw_input(rp, None, None)
+    assert "nasm is NULL" in api.last_error()
+    L.rpool_destroy(rp)
+    nasm.close()
+    dnn.close()
+    capfd.readouterr()
+
+
+def test_corrupt_nasm_file_is_rejected(workdir):
+    cfg, _ = harness.prepare("tiny_cnn", workdir)
+    dnn = api.Dnn(cfg)
+    nasm = api.Nasm(dnn, 1, 0, 4)
+    good = os.path.join(workdir, "good.nasm")
+    nasm.save(good)
+    text = open(good).read()
+    bad = os.path.join(workdir, "bad.nasm")
+    open(bad, "w").write(text.replace("NINST_IDX:5\n", "NINST_IDX:6\n", 1))
+    assert api.lib().apu_load_nasm_from_file(bad.encode(), dnn.h) is None
+    open(bad, "w").write(text[: len(text) // 2])
+    assert api.lib().apu_load_nasm_from_file(bad.encode(), dnn.h) is None
+    nasm.close()
+    dnn.close()
+
+
+def test_engine_refuses_to_run_without_gpu():
+    """No CPU fallback: without a usable sm_100 device a dse group cannot be created."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    assert api.lib().dse_group_init(4) is None
+    assert "CUDA" in api.last_error() or "device" in api.last_error()
