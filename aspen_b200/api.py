@@ -35,7 +35,7 @@ aspen_b200_last_error aspen_b200_group_status aspen_b200_set_tile_profile aspen_
 aspen_b200_set_precision aspen_b200_set_device aspen_b200_dnn_num_layers aspen_b200_dnn_layer_params
 aspen_b200_dnn_layer_type aspen_b200_nasm_num_ldata aspen_b200_nasm_num_ninst aspen_b200_nasm_total_flops
 aspen_b200_nasm_ldata_info aspen_b200_nasm_ninst_info aspen_b200_nasm_ninst_parents aspen_b200_nasm_ninst_children
-aspen_b200_nasm_get_ldata_packed aspen_b200_group_time_runs""".split()
+aspen_b200_nasm_get_ldata_packed aspen_b200_group_time_runs aspen_b200_group_profile""".split()
 
 
 def lib():
@@ -75,6 +75,7 @@ def lib():
         "aspen_b200_nasm_ninst_parents": (u, [vp, u, vp, u]), "aspen_b200_nasm_ninst_children": (u, [vp, u, vp, u]),
         "aspen_b200_nasm_get_ldata_packed": (C.c_long, [vp, u, vp]),
         "aspen_b200_group_time_runs": (C.c_double, [vp, u, u, C.POINTER(C.c_ulonglong)]),
+        "aspen_b200_group_profile": (i, [vp, vp, C.POINTER(u)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -247,6 +248,15 @@ class DseGroup:
         if ms < 0:
             raise RuntimeError("timed runs failed: " + last_error())
         return ms, int(n.value)
+
+    def profile(self):
+        """Scheduler time accounting (needs ASPEN_B200_PROFILE=1): summed nanoseconds and tile counts per layer."""
+        buf = (C.c_ulonglong * 514)()
+        n = C.c_uint(0)
+        if lib().aspen_b200_group_profile(self.h, buf, C.byref(n)) != 0:
+            return None
+        return {"ctas": n.value, "wait_ns": buf[0], "complete_ns": buf[1],
+                "layers": {l: {"ns": buf[2 + l], "tiles": buf[258 + l]} for l in range(256) if buf[258 + l]}}
 
     def close(self):
         if self.h:

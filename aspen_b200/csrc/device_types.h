@@ -21,7 +21,9 @@ struct LayerDev {
     unsigned seq, heads, hd, masked;                     // attention
     unsigned p_out_c, p_in_c, p_stride;                  // yolo / append raw cfg parameters
     const float *anchors;
-    int wmap;                 // index of the weight tensor map, -1 if none
+    int wmap;                 // tensor map of the W-side operand (weights, or PARENT_1 for attention keys), -1 if none
+    int amap;                 // tensor map of the X-side operand (PARENT_0 activations), -1 if gathered
+    unsigned a_kind, b_kind;  // operand staging, see tiles_tc.cuh
     unsigned a_vec4;          // activation rows can be fetched in 16-byte pieces (IC % 4 == 0 ...)
     unsigned round_out;       // store outputs rounded to TF32 (nearest): a tensor-core layer reads them
 };

@@ -48,6 +48,7 @@ struct DeviceDnn {
     std::vector<float *> bias;
     std::vector<float *> anchors;
     std::vector<unsigned> kpad;
+    std::vector<unsigned> ic_pad;     // conv on the network input with IC % 4 != 0: channels padded to this many (0: not padded)
     bool have[2] = {false, false};
 };
 
@@ -72,6 +73,7 @@ static int upload_weights(aspen_dnn_t *dnn, int device, int precision, DeviceDnn
         dd->bias.assign(dnn->num_layers, nullptr);
         dd->anchors.assign(dnn->num_layers, nullptr);
         dd->kpad.assign(dnn->num_layers, 0);
+        dd->ic_pad.assign(dnn->num_layers, 0);
         dnn->dev[device] = dd;
     }
     *out = dd;
@@ -82,14 +84,24 @@ static int upload_weights(aspen_dnn_t *dnn, int device, int precision, DeviceDnn
         if (w) {
             unsigned rows = layer_weight_rows(&l);
             unsigned k = l.type == LAYERNORM_LAYER ? 1 : layer_contraction_k(&l);
-            unsigned kpad = l.type == LAYERNORM_LAYER ? 1 : (unsigned)round_up(k, 32);
+            // A convolution straight on the network input with an odd channel count (the 3-channel
+            // stem): the input matrix keeps its pad rows zero, so the device copy pads every tap to a
+            // multiple of 4 channels with zero weights and the tile reads 16-byte pieces.
+            unsigned ic = l.params[IN_C], icp = ic;
+            if (l.type == CONV_LAYER && l.parent_layers[PARENT_0] && l.parent_layers[PARENT_0]->type == INPUT_LAYER && ic % 4 != 0) {
+                icp = (unsigned)round_up(ic, 4);
+                dd->ic_pad[i] = icp;
+            }
+            const unsigned taps = icp != ic ? k / ic : 1, kk = icp != ic ? taps * icp : k;
+            unsigned kpad = l.type == LAYERNORM_LAYER ? 1 : (unsigned)round_up(kk, 32);
             dd->kpad[i] = kpad;
             std::vector<float> padded((size_t)rows * kpad, 0.f);
             const float *src = (const float *)w->data;
             for (unsigned r = 0; r < rows; r++)
                 for (unsigned c = 0; c < k; c++) {
                     float v = src[(size_t)r * k + c];
-                    padded[(size_t)r * kpad + c] = (precision == 0 && l.type != LAYERNORM_LAYER) ? round_to_tf32(v) : v;
+                    unsigned dc = icp != ic ? (c / ic) * icp + c % ic : c;
+                    padded[(size_t)r * kpad + dc] = (precision == 0 && l.type != LAYERNORM_LAYER) ? round_to_tf32(v) : v;
                 }
             CUDA_TRY(cudaMalloc(&dd->weight[precision][i], padded.size() * sizeof(float) + 256));
             CUDA_TRY(cudaMemcpy(dd->weight[precision][i], padded.data(), padded.size() * sizeof(float), cudaMemcpyHostToDevice));
@@ -145,6 +157,7 @@ struct Engine {
     unsigned long long pipe_ns = 1000000000ull;
     unsigned long long launches = 0;
     float *xfer = nullptr;            // device staging for packed inputs / results
+    unsigned long long *prof = nullptr;   // per-CTA time accounting, allocated when ASPEN_B200_PROFILE is set
     size_t xfer_bytes = 0;
 };
 
@@ -213,7 +226,7 @@ Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) 
     if (env_u64("ASPEN_B200_CTAS", &v) && v > 0 && v <= (unsigned long long)e->num_sms) e->n_ctas = (unsigned)v;
     if (env_u64("ASPEN_B200_STALL_MS", &v) && v > 0) e->stall_ns = v * 1000000ull;
     if (env_u64("ASPEN_B200_PIPE_MS", &v) && v > 0) e->pipe_ns = v * 1000000ull;
-    e->smem_bytes = (precision == 0 ? (size_t)tc::STAGES * tc::STAGE_BYTES : 0) + sizeof(tc::Shared) + 1024;
+    e->smem_bytes = (precision == 0 ? (size_t)tc::STAGES * tc::STAGE_BYTES + tc::EPI_BYTES : 0) + sizeof(tc::Shared) + 1024;
     bool ok = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking) == cudaSuccess &&
               cudaMalloc(&e->ctrl, sizeof(CtrlDev)) == cudaSuccess && cudaMemset(e->ctrl, 0, sizeof(CtrlDev)) == cudaSuccess &&
@@ -225,6 +238,10 @@ Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) 
             ? cudaFuncSetAttribute(sched::scheduler_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes)
             : cudaFuncSetAttribute(sched::scheduler_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes);
         ok = a == cudaSuccess;
+    }
+    if (ok && getenv("ASPEN_B200_PROFILE")) {
+        size_t bytes = (size_t)e->n_ctas * sched::PROF_SLOTS * sizeof(unsigned long long);
+        ok = cudaMalloc(&e->prof, bytes) == cudaSuccess && cudaMemset(e->prof, 0, bytes) == cudaSuccess;
     }
     if (ok && precision == 0 && !get_encode_fn()) { ASPEN_ERR("driver has no cuTensorMapEncodeTiled\n"); ok = false; }
     if (!ok) {
@@ -246,6 +263,7 @@ void engine_destroy(Engine *e) {
     cudaFree(e->queue);
     cudaFree(e->nasms_d);
     cudaFree(e->xfer);
+    cudaFree(e->prof);
     delete e;
 }
 
@@ -315,6 +333,7 @@ static void fill_layer(const nasm_t *nasm, const DeviceNasm *dn, unsigned i, int
     L.IC = p[IN_C]; L.IH = p[IN_H]; L.IW = p[IN_W]; L.OH = p[OUT_H]; L.OW = p[OUT_W];
     L.KH = p[WEIGHT_H]; L.KW = p[WEIGHT_W]; L.stride = p[STRIDE] ? p[STRIDE] : 1; L.pad = p[PADDING];
     if (l.type == FC_LAYER) { L.KH = p[IN_H]; L.KW = p[IN_W]; L.OH = 1; L.OW = 1; L.stride = 1; L.pad = 0; }
+    if (dn->dd->ic_pad[i] && L.ld0 >= dn->dd->ic_pad[i]) { L.IC = dn->dd->ic_pad[i]; L.K = L.KH * L.KW * L.IC; }
     L.seq = nasm->tr_seq_len; L.heads = p[NUM_HEAD]; L.hd = p[NUM_HEAD] ? p[NUM_HIDDEN] / p[NUM_HEAD] : 0; L.masked = p[MASKED];
     L.p_out_c = p[OUT_C]; L.p_in_c = p[IN_C]; L.p_stride = p[STRIDE];
     L.wmap = wmap_idx;
@@ -352,33 +371,71 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
     CUDA_TRY(cudaMalloc(&dn->arena, dn->arena_bytes));
     CUDA_TRY(cudaMemsetAsync(dn->arena, 0, dn->arena_bytes, e->stream));
 
-    // layers + weight tensor maps
+    // layers + tensor maps (weights and, where the access pattern allows it, the parents' activations)
     std::vector<LayerDev> layers(nasm->num_ldata);
     std::vector<CUtensorMap> maps;
+    auto add_map = [&](const void *base, cuuint64_t inner, cuuint64_t outer, cuuint64_t stride_bytes, cuuint32_t box_rows) -> int {
+        CUtensorMap m;
+        cuuint64_t dims[2] = {inner, outer};
+        cuuint64_t strides[1] = {stride_bytes};
+        cuuint32_t box[2] = {32, box_rows}, estr[2] = {1, 1};
+        CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims, strides, box, estr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { ASPEN_ERR("cuTensorMapEncodeTiled failed (%d)\n", (int)r); return -2; }
+        maps.push_back(m);
+        return (int)maps.size() - 1;
+    };
     for (unsigned i = 0; i < nasm->num_ldata; i++) {
         const aspen_layer_t &l = *nasm->ldata[i].layer;
-        int wmap = -1;
+        LayerDev &L = layers[i];
+        fill_layer(nasm, dn, i, e->precision, L, -1);
+        L.amap = -1;
+        L.a_kind = tc::A_GATHER;
+        L.b_kind = tc::B_GATHER;
+        if (e->precision != 0) continue;
         const bool gemm_w = l.type == CONV_LAYER || l.type == FC_LAYER || l.type == MATMUL_LAYER;
-        if (gemm_w && e->precision == 0) {
-            CUtensorMap m;
-            cuuint64_t dims[2] = {dn->dd->kpad[i], layer_weight_rows(&l)};
-            cuuint64_t strides[1] = {(cuuint64_t)dn->dd->kpad[i] * sizeof(float)};
-            cuuint32_t box[2] = {32, 64}, estr[2] = {1, 1};
-            CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dn->dd->weight[0][i], dims, strides, box, estr,
-                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r != CUDA_SUCCESS) { ASPEN_ERR("cuTensorMapEncodeTiled failed (%d) for layer %u\n", (int)r, i); return -1; }
-            wmap = (int)maps.size();
-            maps.push_back(m);
+        const unsigned p0 = nasm->ldata[i].parent_ldata_idx_arr[PARENT_0], p1 = nasm->ldata[i].parent_ldata_idx_arr[PARENT_1];
+        const cuuint64_t W0 = p0 != (unsigned)-1 ? nasm->ldata[p0].out_mat_dims[OUT_W] : 0;
+        if (gemm_w) {
+            L.b_kind = tc::B_TMA;
+            L.wmap = add_map(dn->dd->weight[0][i], dn->dd->kpad[i], layer_weight_rows(&l), (cuuint64_t)dn->dd->kpad[i] * sizeof(float), 64);
+            if (L.wmap < 0) return -1;
         }
-        fill_layer(nasm, dn, i, e->precision, layers[i], wmap);
-        if (e->precision == 0) {
-            const LayerDev &L = layers[i];
-            if (l.type == K_ATTENTION_LAYER && (!L.a_vec4 || L.seq > tc::TMEM_COLS)) {
+        const bool aligned0 = L.ld0 % 4 == 0;
+        if (l.type == MATMUL_LAYER && aligned0 && L.K % 4 == 0) {
+            L.a_kind = tc::A_TMA;
+            L.amap = add_map(L.in0, L.H0, W0, (cuuint64_t)L.ld0 * sizeof(float), 128);
+        } else if (l.type == CONV_LAYER && aligned0 && L.IC % 4 == 0 && L.KH == 1 && L.KW == 1 && L.stride == 1 && L.pad == 0) {
+            L.a_kind = tc::A_TMA;
+            L.amap = add_map(L.in0, L.H0, W0, (cuuint64_t)L.ld0 * sizeof(float), 128);
+        } else if (l.type == CONV_LAYER && aligned0 && L.IC % 32 == 0 && L.stride == 1 && L.OH == L.IH && L.OW == L.IW && L.KH == L.KW &&
+                   2 * L.pad + 1 == L.KH) {
+            L.a_kind = tc::A_TMA_FIXUP;
+            L.amap = add_map(L.in0, L.H0, W0, (cuuint64_t)L.ld0 * sizeof(float), 128);
+        } else if (l.type == FC_LAYER && L.ld0 == L.IC && L.K % 4 == 0) {
+            L.a_kind = tc::A_TMA;   // a sample's NHWC activations are one contiguous row of K values
+            L.amap = add_map(L.in0, L.K, nasm->batch_size, (cuuint64_t)L.IH * L.IW * L.ld0 * sizeof(float), 128);
+        } else if (l.type == K_ATTENTION_LAYER) {
+            if (!L.a_vec4 || L.seq > tc::TMEM_COLS) {
                 ASPEN_ERR("attention_k layer %u: head size must be a multiple of 4 and seq <= %u on the tensor-core path\n", i, tc::TMEM_COLS);
                 return -1;
             }
+            if (L.hd % 32 == 0) {
+                L.a_kind = tc::A_TMA;
+                L.amap = add_map(L.in0, L.H0, W0, (cuuint64_t)L.ld0 * sizeof(float), 128);
+                L.b_kind = tc::B_TMA_ACT;
+                L.wmap = add_map(L.in1, L.H1, nasm->ldata[p1].out_mat_dims[OUT_W], (cuuint64_t)L.ld1 * sizeof(float), 64);
+                if (L.wmap < 0) return -1;
+            }
+        } else if (l.type == V_ATTENTION_LAYER) {
+            L.b_kind = tc::B_TRANSPOSED;
+            if (aligned0) {
+                L.a_kind = tc::A_TMA;
+                L.amap = add_map(L.in0, L.H0, W0, (cuuint64_t)L.ld0 * sizeof(float), 128);
+            }
         }
+        if (L.a_kind != tc::A_GATHER && L.amap < 0) return -1;
     }
     if (e->precision == 0) {
         for (unsigned i = 0; i < nasm->num_ldata; i++) {
@@ -557,9 +614,9 @@ static int launch_run(Engine *e, const std::vector<nasm_t *> &run) {
     sched::arm_kernel<<<arm_blocks, 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue, total, n_init, n_input, e->stall_ns, e->pipe_ns);
     sched::seed_kernel<<<std::max(1u, std::min<unsigned>((n_init + 255) / 256, 256)), 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue);
     if (e->precision == 0)
-        sched::scheduler_kernel<true><<<e->n_ctas, tc::NTHREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d);
+        sched::scheduler_kernel<true><<<e->n_ctas, tc::NTHREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
     else
-        sched::scheduler_kernel<false><<<e->n_ctas, tc::NTHREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d);
+        sched::scheduler_kernel<false><<<e->n_ctas, tc::NTHREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
     e->launches += 3;
     CUDA_TRY(cudaGetLastError());
     return 0;
@@ -672,3 +729,18 @@ double engine_time_runs(Engine *e, const std::vector<nasm_t *> &nasms, unsigned 
 }
 
 void engine_flush() {}
+
+// Sums the per-CTA time accounting (ASPEN_B200_PROFILE=1) into out[PROF_SLOTS] and clears it.
+int engine_read_profile(Engine *e, unsigned long long *out, unsigned *n_ctas) {
+    if (!e || !e->prof) return -1;
+    CUDA_TRY(cudaSetDevice(e->device));
+    CUDA_TRY(cudaStreamSynchronize(e->stream));
+    std::vector<unsigned long long> h((size_t)e->n_ctas * sched::PROF_SLOTS);
+    CUDA_TRY(cudaMemcpy(h.data(), e->prof, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    CUDA_TRY(cudaMemset(e->prof, 0, h.size() * sizeof(unsigned long long)));
+    for (unsigned s = 0; s < sched::PROF_SLOTS; s++) out[s] = 0;
+    for (unsigned c = 0; c < e->n_ctas; c++)
+        for (unsigned s = 0; s < sched::PROF_SLOTS; s++) out[s] += h[(size_t)c * sched::PROF_SLOTS + s];
+    if (n_ctas) *n_ctas = e->n_ctas;
+    return 0;
+}

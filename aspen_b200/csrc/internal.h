@@ -159,3 +159,4 @@ long engine_read_ldata(nasm_t *nasm, unsigned int ldata_idx, float *out_packed);
 double engine_time_runs(Engine *e, const std::vector<nasm_t *> &nasms, unsigned int warmup, unsigned int iters, unsigned long long *launches);
 void engine_release_dnn(aspen_dnn_t *dnn);
 void engine_flush();
+int engine_read_profile(Engine *e, unsigned long long *out, unsigned *n_ctas);

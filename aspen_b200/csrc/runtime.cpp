@@ -175,6 +175,10 @@ extern "C" double aspen_b200_group_time_runs(dse_group_t *g, unsigned int warmup
     return engine_time_runs(g->engine, g->rpool->nasms, warmup, iters, launches);
 }
 
+extern "C" int aspen_b200_group_profile(dse_group_t *g, unsigned long long *out64, unsigned int *n_ctas) {
+    return g ? engine_read_profile(g->engine, out64, n_ctas) : -1;
+}
+
 extern "C" void aspen_flush_dynamic_memory(void) { engine_flush(); }
 
 extern "C" int aspen_b200_set_device(int device);   // engine.cu

@@ -26,6 +26,9 @@
 
 namespace sched {
 
+constexpr unsigned PROF_LAYERS = 256;
+constexpr unsigned PROF_SLOTS = 2 + 2 * PROF_LAYERS;
+
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -102,7 +105,7 @@ __device__ unsigned complete_tile(const NasmDev &G, unsigned local, CtrlDev *ctr
         }
         unsigned mask = __ballot_sync(0xffffffffu, ready);
         if (mask == 0u) continue;
-        __threadfence();                                 // acquire the other parents' outputs, then publish
+        __threadfence();                                 // acquire the other parents' outputs (through the counters), then publish
         if (next == ASPEN_TILE_NONE) {
             const unsigned first = __ffs(mask) - 1u;
             next = __shfl_sync(0xffffffffu, child, first) + G.tile_base;
@@ -178,18 +181,18 @@ __device__ __forceinline__ void run_tile(const LayerDev &L, const TileDev &T, co
 
 template <bool TENSOR_CORES>
 __global__ void __launch_bounds__(tc::NTHREADS, 1)
-scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHost *status) {
+scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHost *status, unsigned long long *prof) {
     extern __shared__ unsigned char smem_raw[];
     // stage buffers need 1024-byte alignment for the 128-byte swizzle
     unsigned char *stage_mem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
-    tc::Shared *sh = reinterpret_cast<tc::Shared *>(stage_mem + (TENSOR_CORES ? tc::STAGES * tc::STAGE_BYTES : 0u));
+    tc::Shared *sh = reinterpret_cast<tc::Shared *>(stage_mem + (TENSOR_CORES ? tc::STAGES * tc::STAGE_BYTES + tc::EPI_BYTES : 0u));
     const unsigned tid = threadIdx.x, warp = tid >> 5;
     const unsigned ctrl_warp = tc::NW >> 5;
     tc::PipeState ps;
 
     if (TENSOR_CORES) {
         if (tid == 0) {
-            for (int s = 0; s < tc::STAGES; s++) { tc::mbar_init(&sh->full[s], tc::NW + 1u); tc::mbar_init(&sh->empty[s], 1u); }
+            for (int s = 0; s < tc::STAGES; s++) { tc::mbar_init(&sh->full[s], tc::NW); tc::mbar_init(&sh->empty[s], 1u); tc::mbar_init(&sh->landed[s], 1u); }
             tc::mbar_init(&sh->accum, 1u);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             tc::fence_proxy_async_smem();
@@ -202,8 +205,16 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
 
     const unsigned n_nasm = ctrl->n_nasm;
     unsigned next = ASPEN_TILE_NONE;
+    // Optional time accounting (per CTA, by the control thread): [0] waiting for a ready tile,
+    // [1] completion + child update, [2 + layer] running tiles of that layer (index modulo PROF_LAYERS),
+    // [2 + PROF_LAYERS + layer] tile counts.
+    unsigned long long *my_prof = prof ? prof + (size_t)blockIdx.x * PROF_SLOTS : nullptr;
+    unsigned long long t_mark = my_prof ? global_ns() : 0ull;
     while (true) {
-        if (tid == tc::TMA_THREAD) sh->tile = next != ASPEN_TILE_NONE ? next : pop_ready(ctrl, queue, status);
+        if (tid == tc::TMA_THREAD) {
+            sh->tile = next != ASPEN_TILE_NONE ? next : pop_ready(ctrl, queue, status);
+            if (my_prof) { unsigned long long now = global_ns(); my_prof[0] += now - t_mark; t_mark = now; }
+        }
         __syncthreads();
         const unsigned gid = sh->tile;
         if (gid == ASPEN_TILE_NONE) break;
@@ -216,8 +227,13 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
         run_tile<TENSOR_CORES>(L, T, G, stage_mem, sh, ps, ctrl, status);
         __syncthreads();                                  // every thread's stores of this tile are issued
         if (warp == ctrl_warp) {
+            if (my_prof && tid == tc::TMA_THREAD) {
+                unsigned long long now = global_ns();
+                my_prof[2 + T.layer % PROF_LAYERS] += now - t_mark; my_prof[2 + PROF_LAYERS + T.layer % PROF_LAYERS] += 1ull; t_mark = now;
+            }
             next = ASPEN_TILE_NONE;
             if (!ps.dead && !sched::ld_relaxed(&ctrl->abort)) next = complete_tile(G, local, ctrl, queue, status);
+            if (my_prof && tid == tc::TMA_THREAD) { unsigned long long now = global_ns(); my_prof[1] += now - t_mark; t_mark = now; }
         }
     }
 

@@ -17,7 +17,7 @@ extern "C" void aspen_b200_set_tile_quanta(unsigned int h_min, unsigned int w_mi
     g_quanta.flop_per_ninst = flop_per_ninst ? flop_per_ninst : 100000000u;
 }
 extern "C" void aspen_b200_set_tile_profile(int profile) {
-    if (profile == 1) aspen_b200_set_tile_quanta(64, 128, 100000000u);
+    if (profile == 1) aspen_b200_set_tile_quanta(128, 128, 100000000u);
     else aspen_b200_set_tile_quanta(NINST_H_MIN, NINST_W_MIN, 100000000u);
 }
 

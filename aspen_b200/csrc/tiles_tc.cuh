@@ -37,10 +37,12 @@ constexpr unsigned TMA_THREAD = NW;          // lane 0 of warp 8
 constexpr unsigned MMA_THREAD = NW + 32;     // lane 0 of warp 9
 constexpr unsigned NTHREADS = NW + 64;
 constexpr unsigned TMEM_COLS = 512;
+constexpr unsigned EPI_BYTES = (NW / 32) * 4096;   // per-warp transpose staging of the epilogue
 
 struct Shared {
     unsigned long long full[STAGES];
     unsigned long long empty[STAGES];
+    unsigned long long landed[STAGES];   // TMA bytes of a stage have arrived
     unsigned long long accum;
     unsigned tmem_base;
     unsigned tile;            // scheduler mailbox
@@ -50,6 +52,7 @@ struct Shared {
 struct PipeState {            // identical in every thread, carried across tiles
     unsigned it = 0;          // k-chunk iterations issued so far
     unsigned acc_phase = 0;   // accumulator barrier phase
+    unsigned full_phase = 0;  // MMA thread: per-stage phase bits of the "full" barriers (not every layer uses them)
     bool dead = false;
 };
 
@@ -156,19 +159,62 @@ __device__ __forceinline__ unsigned umma_idesc(unsigned n) {
 
 __device__ __forceinline__ unsigned swz(unsigned row, unsigned piece) { return row * 128u + ((piece ^ (row & 7u)) << 4); }
 
+// Writes one 32 (tile columns n, one per lane) x 32 (rows m, in v[]) block of a warp's results.
+// Each lane holds 32 consecutive m of ITS column, but global memory wants consecutive m from
+// consecutive lanes, so the block is transposed through a 4 KB per-warp staging area (XOR-swizzled
+// 16-byte pieces, conflict free both ways): every store instruction then covers four full 128-byte lines
+// instead of 32 scattered 16-byte pieces.
+__device__ __forceinline__ void store_block_coalesced(float *stage /*warp's 4 KB*/, const float *v, float *out_block /*(n = 0, m = 0)*/,
+                                                      size_t ldc, unsigned n_valid, unsigned m_valid) {
+    const unsigned lane = threadIdx.x & 31u;
+    float4 *st = reinterpret_cast<float4 *>(stage);
+    #pragma unroll
+    for (unsigned j = 0; j < 8; j++) st[lane * 8u + (j ^ (lane & 7u))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    __syncwarp();
+    const unsigned piece = lane & 7u, m = piece * 4u;
+    #pragma unroll
+    for (unsigned i = 0; i < 8; i++) {
+        const unsigned n = i * 4u + (lane >> 3);
+        const float4 val = st[n * 8u + (piece ^ (n & 7u))];
+        if (n < n_valid) {
+            float *dst = out_block + (size_t)n * ldc + m;
+            if (m + 4u <= m_valid) *reinterpret_cast<float4 *>(dst) = val;
+            else {
+                if (m < m_valid) dst[0] = val.x;
+                if (m + 1u < m_valid) dst[1] = val.y;
+                if (m + 2u < m_valid) dst[2] = val.z;
+            }
+        }
+    }
+    __syncwarp();
+}
+
 // ---- per-layer operand description -------------------------------------------------------------
+// How the two operands of a layer reach shared memory (chosen on the host, LayerDev::a_kind / b_kind):
+//   X side  A_GATHER     worker threads, cp.async per 16-byte piece (4-byte pieces when IC % 4 != 0): strided
+//                        convolutions, the 3-channel stem, connected layers over a padded parent
+//           A_TMA        one 32 x 128 box per k-chunk straight from the parent's [columns][rows] matrix:
+//                        matmul, 1x1 stride-1 convolution, attention, connected layers over an unpadded parent
+//           A_TMA_FIXUP  stride-1 "same" convolution: tap (kh, kw) of 128 consecutive output pixels is the parent
+//                        matrix shifted by (kh-p)*IW + (kw-p) columns, except where the tap leaves the image; the
+//                        box is loaded shifted and the owner thread of each such row overwrites it with zeros
+//   W side  B_TMA        64-row boxes of the [rows][Kpad] weight copy
+//           B_TMA_ACT    64-row boxes of the PARENT_1 activation matrix (attention keys)
+//           B_GATHER     cp.async rows of PARENT_1 (attention keys whose head size is not a multiple of 32)
+//           B_TRANSPOSED 4-byte cp.async transposing gather (attention values: W(m,k) = V[token k][feature m])
+enum { A_GATHER = 0, A_TMA = 1, A_TMA_FIXUP = 2 };
+enum { B_GATHER = 0, B_TMA = 1, B_TMA_ACT = 2, B_TRANSPOSED = 3 };
+
 struct Operands {
-    // X (activation) side
-    const float *xrow;        // row-pointer kinds: start of column 0 of the tile; row n at xrow + n * xld
+    const float *xrow;        // A_GATHER row-pointer layers: row n at xrow + n * xld
     size_t xld;
-    bool conv;                // taps gathered from L.in0
-    // W side
-    bool tma;                 // weights by TMA
-    bool transposed;          // V-attention: W(m,k) = wbase[k * wld + m]
-    const float *wbase;       // gathered kinds: row m at wbase + m * wld
+    bool conv;                // taps taken from L.in0 (convolution, connected)
+    const float *wbase;       // gathered W: row m at wbase + m * wld (B_GATHER) or wbase[k * wld + m] (B_TRANSPOSED)
     size_t wld;
     unsigned w_rows;          // rows that exist (others read as zero)
     unsigned K, Kpad;
+    int ax, ay;               // A_TMA: box coordinates of (column n0 = 0, k = 0)
+    int bx, by;               // B_TMA / B_TMA_ACT: coordinates of (row 0 of the tile, k = 0)
     bool softmax;             // K-attention epilogue
     bool plain;               // V-attention epilogue: no bias / activation
     unsigned q0;              // K-attention: query index of tile column 0
@@ -176,27 +222,31 @@ struct Operands {
 
 __device__ __forceinline__ Operands make_operands(const LayerDev &L, const TileDev &T) {
     Operands o;
-    o.conv = false; o.tma = false; o.transposed = false; o.softmax = false; o.plain = false; o.q0 = 0;
+    o.conv = false; o.softmax = false; o.plain = false; o.q0 = 0;
     o.xrow = nullptr; o.xld = 0; o.wbase = nullptr; o.wld = 0; o.w_rows = T.tile_h;
+    o.ax = 0; o.ay = (int)T.pos_w; o.bx = 0; o.by = (int)T.pos_h;
     switch (L.type) {
         case CONV_LAYER: case FC_LAYER:
-            o.conv = true; o.tma = true; o.K = L.K; o.Kpad = L.Kpad;
+            o.conv = true; o.K = L.K; o.Kpad = L.Kpad;
             break;
         case MATMUL_LAYER:
-            o.xrow = L.in0 + (size_t)T.pos_w * L.ld0; o.xld = L.ld0; o.tma = true; o.K = L.K; o.Kpad = L.Kpad;
+            o.xrow = L.in0 + (size_t)T.pos_w * L.ld0; o.xld = L.ld0; o.K = L.K; o.Kpad = L.Kpad;
             break;
         case K_ATTENTION_LAYER: {
             unsigned b = T.pos_w / (L.seq * L.heads), head = (T.pos_w % (L.seq * L.heads)) / L.seq;
             o.q0 = T.pos_w % L.seq;
             o.xrow = L.in0 + (size_t)(b * L.seq + o.q0) * L.ld0 + head * L.hd; o.xld = L.ld0;
             o.wbase = L.in1 + (size_t)(b * L.seq + T.pos_h) * L.ld1 + head * L.hd; o.wld = L.ld1;
+            o.ax = (int)(head * L.hd); o.ay = (int)(b * L.seq + o.q0);
+            o.bx = (int)(head * L.hd); o.by = (int)(b * L.seq + T.pos_h);
             o.K = L.hd; o.Kpad = (L.hd + 31u) & ~31u; o.softmax = true;
             break;
         }
         default: {   // V_ATTENTION_LAYER
             unsigned b = T.pos_w / L.seq, head = T.pos_h / L.hd, q0 = T.pos_w % L.seq;
             o.xrow = L.in0 + (size_t)((b * L.heads + head) * L.seq + q0) * L.ld0; o.xld = L.ld0;
-            o.wbase = L.in1 + (size_t)b * L.seq * L.ld1 + T.pos_h; o.wld = L.ld1; o.transposed = true;
+            o.ay = (int)((b * L.heads + head) * L.seq + q0);
+            o.wbase = L.in1 + (size_t)b * L.seq * L.ld1 + T.pos_h; o.wld = L.ld1;
             o.K = L.seq; o.Kpad = (L.seq + 31u) & ~31u; o.plain = true;
             break;
         }
@@ -205,7 +255,7 @@ __device__ __forceinline__ Operands make_operands(const LayerDev &L, const TileD
 }
 
 // One ninst tile.  Called by all NTHREADS threads of the CTA.
-__device__ void tile_gemm(const LayerDev &L, const TileDev &T, const NasmDev &G, unsigned char *stage_mem, Shared *sh,
+__device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDev &G, unsigned char *stage_mem, Shared *sh,
                           PipeState &ps, CtrlDev *ctrl, StatusHost *status) {
     const unsigned tid = threadIdx.x;
     const bool is_worker = tid < NW;
@@ -213,7 +263,11 @@ __device__ void tile_gemm(const LayerDev &L, const TileDev &T, const NasmDev &G,
     const Operands op = make_operands(L, T);
     const unsigned stage_base = smem_u32(stage_mem);
     const unsigned tmem = sh->tmem_base;
-    const void *tmap = op.tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.wmap * 128) : nullptr;
+    const unsigned a_kind = L.a_kind, b_kind = L.b_kind;
+    const bool a_tma = a_kind != A_GATHER, b_tma = b_kind == B_TMA || b_kind == B_TMA_ACT;
+    const bool worker_work = a_kind != A_TMA || !b_tma;      // workers write shared memory in this layer
+    const void *amap = a_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.amap * 128) : nullptr;
+    const void *bmap = b_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.wmap * 128) : nullptr;
     const bool vec_x = L.a_vec4 != 0;
 
     for (unsigned n0 = 0; n0 < T.tile_w; n0 += 128) {
@@ -221,25 +275,45 @@ __device__ void tile_gemm(const LayerDev &L, const TileDev &T, const NasmDev &G,
         const bool row_ok = row < rows_valid;
         PixelWin pw = {0, 0, 0};
         const float *xr = nullptr;
-        if (is_worker && row_ok) {
+        if (is_worker) {
             if (op.conv) pw = pixel_window(L, T.pos_w + n0 + row);
-            else xr = op.xrow + (size_t)(n0 + row) * op.xld;
+            else if (row_ok && a_kind == A_GATHER) xr = op.xrow + (size_t)(n0 + row) * op.xld;
         }
         for (unsigned ms = 0; ms < T.tile_h; ms += TMEM_COLS) {
             const unsigned cols_super = min(TMEM_COLS, T.tile_h - ms);
             unsigned arrived = ps.it;            // next iteration this worker still owes a "full" arrival for
             for (unsigned mp = 0; mp < cols_super; mp += 256) {
                 const unsigned nb = min(256u, cols_super - mp);
-                const unsigned NB = op.tma ? ((nb + 63u) & ~63u) : ((nb + 15u) & ~15u);
+                const unsigned NB = b_tma ? ((nb + 63u) & ~63u) : ((nb + 15u) & ~15u);
                 for (unsigned kc = 0; kc < op.Kpad; kc += 32, ps.it++) {
                     const unsigned s = ps.it % STAGES, ph = (ps.it / STAGES) & 1u;
                     const unsigned sA = stage_base + s * STAGE_BYTES, sB = sA + A_STAGE_BYTES;
                     if (is_worker) {
+                        if (!worker_work) continue;
+                        if (a_kind == A_TMA_FIXUP) {
+                            // the shifted box has landed: rows whose tap is outside the image become zero
+                            if (!ps.dead && !mbar_wait(&sh->landed[s], ph, ctrl, status, 5)) ps.dead = true;
+                            ps.dead = __any_sync(0xffffffffu, ps.dead);
+                            if (!ps.dead && half == 0) {
+                                const unsigned tap = kc / L.IC;
+                                const int ih = pw.ih0 + (int)(tap / L.KW), iw = pw.iw0 + (int)(tap % L.KW);
+                                if (ih < 0 || ih >= (int)L.IH || iw < 0 || iw >= (int)L.IW) {
+                                    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                                    float4 *dst = reinterpret_cast<float4 *>(stage_mem + s * STAGE_BYTES + row * 128u);
+                                    #pragma unroll
+                                    for (int c = 0; c < 8; c++) dst[c] = z;
+                                }
+                            }
+                            fence_proxy_async_smem();
+                            if (!ps.dead) mbar_arrive(&sh->full[s]);
+                            arrived = ps.it + 1;
+                            continue;
+                        }
                         if (!ps.dead && !mbar_wait(&sh->empty[s], ph ^ 1u, ctrl, status, 1)) ps.dead = true;
                         ps.dead = __any_sync(0xffffffffu, ps.dead);   // keep worker warps convergent on the failure path
                         if (!ps.dead) {
                             // ---- X side: this thread's half (4 pieces / 16 elements) of its row ----
-                            if (row_ok) {
+                            if (a_kind == A_GATHER && row_ok) {
                                 if (vec_x) {
                                     #pragma unroll
                                     for (unsigned c = 0; c < 4; c++) {
@@ -271,20 +345,18 @@ __device__ void tile_gemm(const LayerDev &L, const TileDev &T, const NasmDev &G,
                                     }
                                 }
                             }
-                            // ---- W side when it is not a TMA operand ----
-                            if (!op.tma) {
-                                if (!op.transposed) {
-                                    for (unsigned i = tid; i < NB * 8; i += NW) {
-                                        const unsigned r = i >> 3, piece = i & 7u, k = kc + piece * 4, m = ms + mp + r;
-                                        const bool ok = m < op.w_rows && k < op.K;
-                                        cp_async16(sB + swz(r, piece), ok ? op.wbase + (size_t)m * op.wld + k : L.in1, ok ? 16u : 0u);
-                                    }
-                                } else {
-                                    for (unsigned i = tid; i < NB * 32; i += NW) {
-                                        const unsigned r = i % NB, kk = i / NB, k = kc + kk, m = ms + mp + r;
-                                        const bool ok = m < op.w_rows && k < op.K;
-                                        cp_async4(sB + swz(r, kk >> 2) + (kk & 3u) * 4u, ok ? op.wbase + (size_t)k * op.wld + m : L.in1, ok ? 4u : 0u);
-                                    }
+                            // ---- W side when it is gathered ----
+                            if (b_kind == B_GATHER) {
+                                for (unsigned i = tid; i < NB * 8; i += NW) {
+                                    const unsigned r = i >> 3, piece = i & 7u, k = kc + piece * 4, m = ms + mp + r;
+                                    const bool ok = m < op.w_rows && k < op.K;
+                                    cp_async16(sB + swz(r, piece), ok ? op.wbase + (size_t)m * op.wld + k : L.in1, ok ? 16u : 0u);
+                                }
+                            } else if (b_kind == B_TRANSPOSED) {
+                                for (unsigned i = tid; i < NB * 32; i += NW) {
+                                    const unsigned r = i % NB, kk = i / NB, k = kc + kk, m = ms + mp + r;
+                                    const bool ok = m < op.w_rows && k < op.K;
+                                    cp_async4(sB + swz(r, kk >> 2) + (kk & 3u) * 4u, ok ? op.wbase + (size_t)k * op.wld + m : L.in1, ok ? 4u : 0u);
                                 }
                             }
                         }
@@ -298,16 +370,28 @@ __device__ void tile_gemm(const LayerDev &L, const TileDev &T, const NasmDev &G,
                     } else if (tid == TMA_THREAD) {
                         if (!ps.dead && !mbar_wait(&sh->empty[s], ph ^ 1u, ctrl, status, 2)) ps.dead = true;
                         if (!ps.dead) {
-                            if (op.tma) {
-                                mbar_arrive_expect_tx(&sh->full[s], NB * 128u);
-                                for (unsigned j = 0; j < NB; j += 64)
-                                    tma_load_2d(sB + j * 128u, tmap, (int)kc, (int)(T.pos_h + ms + mp + j), &sh->full[s]);
-                            } else {
-                                mbar_arrive(&sh->full[s]);
+                            const unsigned bytes = (a_tma ? A_STAGE_BYTES : 0u) + (b_tma ? NB * 128u : 0u);
+                            if (bytes) mbar_arrive_expect_tx(&sh->landed[s], bytes);
+                            else mbar_arrive(&sh->landed[s]);
+                            if (a_tma) {
+                                int x = op.ax + (int)kc, y = op.ay + (int)n0;
+                                if (a_kind == A_TMA_FIXUP) {
+                                    const unsigned tap = kc / L.IC;
+                                    x = (int)(kc - tap * L.IC);
+                                    y += ((int)(tap / L.KW) - (int)L.pad) * (int)L.IW + ((int)(tap % L.KW) - (int)L.pad);
+                                }
+                                tma_load_2d(sA, amap, x, y, &sh->landed[s]);
                             }
+                            if (b_tma)
+                                for (unsigned j = 0; j < NB; j += 64)
+                                    tma_load_2d(sB + j * 128u, bmap, op.bx + (int)kc, op.by + (int)(ms + mp + j), &sh->landed[s]);
                         }
                     } else if (tid == MMA_THREAD) {
-                        if (!ps.dead && !mbar_wait(&sh->full[s], ph, ctrl, status, 3)) ps.dead = true;
+                        if (!ps.dead && !mbar_wait(&sh->landed[s], ph, ctrl, status, 3)) ps.dead = true;
+                        if (worker_work) {
+                            if (!ps.dead && !mbar_wait(&sh->full[s], (ps.full_phase >> s) & 1u, ctrl, status, 6)) ps.dead = true;
+                            ps.full_phase ^= 1u << s;
+                        }
                         if (!ps.dead) {
                             tc_fence_after();
                             const unsigned long long adesc = umma_desc(sA), bdesc = umma_desc(sB);
@@ -323,17 +407,22 @@ __device__ void tile_gemm(const LayerDev &L, const TileDev &T, const NasmDev &G,
             // ---- all k-chunks of this 128 x cols_super block are issued ----
             if (tid == MMA_THREAD && !ps.dead) tc_commit(&sh->accum);
             if (is_worker) {
-                cp_async_wait<0>();
-                fence_proxy_async_smem();
-                for (; arrived != ps.it; arrived++)
-                    if (!ps.dead) mbar_arrive(&sh->full[arrived % STAGES]);
+                if (worker_work && a_kind != A_TMA_FIXUP) {
+                    cp_async_wait<0>();
+                    fence_proxy_async_smem();
+                    for (; arrived != ps.it; arrived++)
+                        if (!ps.dead) mbar_arrive(&sh->full[arrived % STAGES]);
+                }
                 if (!ps.dead && !mbar_wait(&sh->accum, ps.acc_phase, ctrl, status, 4)) ps.dead = true;
                 ps.dead = __any_sync(0xffffffffu, ps.dead);
                 tc_fence_after();
                 // ---- epilogue: thread = output column n0 + row, this half's 32-wide row chunks ----
                 const unsigned lane_base = ((tid >> 5) & 3u) * 32u;
                 const unsigned nchunk = (cols_super + 31u) >> 5;
-                float *ocol = L.out + (size_t)(T.pos_w + n0 + row) * L.ldc + T.pos_h + ms;
+                // block (n = first column of this warp's 32, m = ms) of the output matrix
+                float *oblk = L.out + (size_t)(T.pos_w + n0 + lane_base) * L.ldc + T.pos_h + ms;
+                const unsigned n_valid = rows_valid > lane_base ? rows_valid - lane_base : 0u;
+                float *epi = reinterpret_cast<float *>(stage_mem + STAGES * STAGE_BYTES) + (tid >> 5) * 1024u;
                 float v[32];
                 if (op.softmax) {
                     // scores -> mask -> / sqrt(hd) -> exp, normalised by the column sum (ref src/tiled_kernels.c:859-876)
@@ -362,40 +451,44 @@ __device__ void tile_gemm(const LayerDev &L, const TileDev &T, const NasmDev &G,
                             float x = (L.masked && (T.pos_h + m) > q) ? -1e10f : v[j];
                             v[j] = store_round(expf(x / scale) / sum, L);
                         }
-                        if (row_ok && !ps.dead) {
-                            #pragma unroll
-                            for (unsigned j = 0; j < 32; j++)
-                                if (ms + c * 32u + j < T.tile_h) ocol[c * 32u + j] = v[j];
-                        }
+                        if (!ps.dead) store_block_coalesced(epi, v, oblk + c * 32u, L.ldc, n_valid, min(32u, cols_super - c * 32u));
                     }
                     worker_barrier(NW);   // partial[] is reused by the next block
                 } else {
                     const float *bias = (!op.plain && L.bias) ? L.bias + T.pos_h + ms : nullptr;
+                    const bool bias_vec = bias && ((reinterpret_cast<uintptr_t>(bias) & 15u) == 0u);
+                    const int act = L.act;
+                    const bool rnd = L.round_out != 0;
                     for (unsigned c = half; c < nchunk; c += 2) {
                         if (!ps.dead) tmem_ld32(tmem + (lane_base << 16) + c * 32u, v);
                         const unsigned valid = min(32u, cols_super - c * 32u);
-                        if (!op.plain) {
-                            #pragma unroll
-                            for (unsigned j = 0; j < 32; j++) {
-                                float x = v[j];
-                                if (bias && j < valid) x += __ldg(bias + c * 32u + j);
-                                v[j] = finish(x, L);
-                            }
-                        } else {
-                            #pragma unroll
-                            for (unsigned j = 0; j < 32; j++) v[j] = store_round(v[j], L);
-                        }
-                        if (row_ok && !ps.dead) {
-                            if (valid == 32u) {
+                        if (bias) {
+                            if (bias_vec && valid == 32u) {
                                 #pragma unroll
-                                for (unsigned j = 0; j < 32; j += 4)
-                                    *reinterpret_cast<float4 *>(ocol + c * 32u + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                for (unsigned j = 0; j < 32; j += 4) {
+                                    const float4 b4 = __ldg(reinterpret_cast<const float4 *>(bias + c * 32u + j));
+                                    v[j] += b4.x; v[j + 1] += b4.y; v[j + 2] += b4.z; v[j + 3] += b4.w;
+                                }
                             } else {
                                 #pragma unroll
                                 for (unsigned j = 0; j < 32; j++)
-                                    if (j < valid) ocol[c * 32u + j] = v[j];
+                                    if (j < valid) v[j] += __ldg(bias + c * 32u + j);
                             }
                         }
+                        if (!op.plain) {
+                            if (act == RELU) {
+                                #pragma unroll
+                                for (unsigned j = 0; j < 32; j++) v[j] = fmaxf(v[j], 0.f);
+                            } else if (act != NO_ACTIVATION && act != LINEAR) {
+                                #pragma unroll
+                                for (unsigned j = 0; j < 32; j++) v[j] = activate(v[j], act);
+                            }
+                        }
+                        if (rnd) {
+                            #pragma unroll
+                            for (unsigned j = 0; j < 32; j++) v[j] = tf32_round(v[j]);
+                        }
+                        if (!ps.dead) store_block_coalesced(epi, v, oblk + c * 32u, L.ldc, n_valid, valid);
                     }
                 }
                 tc_fence_before();

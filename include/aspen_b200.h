@@ -159,8 +159,8 @@ const char *aspen_b200_last_error(void);
 int aspen_b200_group_status(dse_group_t *dse_group);
 
 /* Tiler profile.  The reference's constants (64-row / 12-column quanta, 1e8 flop per tile) shape
- * tiles for an 8x12 AVX2 register block; profile 1 uses 64-row / 128-column quanta so a tile is
- * whole 128-row tensor-core blocks.  Tile VALUES do not depend on the profile.  Affects nasms
+ * tiles for an 8x12 AVX2 register block; profile 1 uses 128-row / 128-column quanta so a tile is
+ * whole 128 x 128 tensor-core blocks.  Tile VALUES do not depend on the profile.  Affects nasms
  * created afterwards.  0 = reference geometry (default), 1 = B200 geometry. */
 void aspen_b200_set_tile_profile(int profile);
 void aspen_b200_set_tile_quanta(unsigned int h_min, unsigned int w_min, unsigned int flop_per_ninst);
@@ -196,6 +196,13 @@ long aspen_b200_nasm_get_ldata_packed(nasm_t *nasm, unsigned int ldata_idx, floa
  * milliseconds measured with CUDA events on the group's stream; *launches_out (may be NULL) gets
  * the number of kernel launches issued.  Returns a negative value on error. */
 double aspen_b200_group_time_runs(dse_group_t *dse_group, unsigned int warmup, unsigned int iters, unsigned long long *launches_out);
+
+/* Time accounting of the device scheduler (replaces the reference's wall-clock probes,
+ * ref src/util.c:490-539).  Active when the environment variable ASPEN_B200_PROFILE is set before
+ * dse_group_init.  out[514], nanoseconds summed over all worker CTAs since the last call:
+ * [0] waiting for a ready tile, [1] completion and child update, [2 + l] running tiles of layer l
+ * (l modulo 256), [258 + l] number of tiles of layer l.  Returns 0, or -1 when inactive. */
+int aspen_b200_group_profile(dse_group_t *dse_group, unsigned long long *out, unsigned int *n_ctas);
 
 #ifdef __cplusplus
 }

@@ -58,7 +58,8 @@ class Device:
     def __init__(self, cfg: str, wfile: str | None, batch: int, seq: int = 0, min_ninst: int = 100, precision: int = 0,
                  profile: int = 0):
         L = api.lib()
-        L.aspen_b200_set_tile_profile(profile)
+        if profile in (0, 1):
+            L.aspen_b200_set_tile_profile(profile)   # any other value: keep the quanta the caller has set
         self.dnn = api.Dnn(cfg, wfile)
         self.nasm = api.Nasm(self.dnn, batch, seq, min_ninst)
         L.aspen_b200_set_tile_profile(0)
