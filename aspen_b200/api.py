@@ -251,11 +251,11 @@ class DseGroup:
 
     def profile(self):
         """Scheduler time accounting (needs ASPEN_B200_PROFILE=1): summed nanoseconds and tile counts per layer."""
-        buf = (C.c_ulonglong * 514)()
+        buf = (C.c_ulonglong * 516)()
         n = C.c_uint(0)
         if lib().aspen_b200_group_profile(self.h, buf, C.byref(n)) != 0:
             return None
-        return {"ctas": n.value, "wait_ns": buf[0], "complete_ns": buf[1],
+        return {"ctas": n.value, "idle_polls": buf[0], "complete_ns": buf[1], "wait_ns": buf[515],
                 "layers": {l: {"ns": buf[2 + l], "tiles": buf[258 + l]} for l in range(256) if buf[258 + l]}}
 
     def close(self):

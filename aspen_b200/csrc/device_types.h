@@ -39,7 +39,7 @@ struct TileDev {
 struct NasmDev {
     const LayerDev *layers;
     const TileDev *tiles;
-    const unsigned *children;        // CSR payload: local tile ids
+    const unsigned *children;        // CSR payload: (local child tile id, count that child waits for) pairs
     unsigned *dep;                   // [n_tiles] parents completed so far
     const unsigned *dep_init;        // [n_tiles] parents that are input tiles (complete when armed)
     unsigned *layer_done;            // [n_layers] tiles completed per layer

@@ -455,7 +455,11 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
         if (!maps.empty()) CUDA_TRY(cudaMemcpy(dn->wmaps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
     }
 
-    // tiles, children (CSR over true dependencies = listed parents + supplement), counters
+    // tiles, children (CSR), counters.  A tile's count to reach is the length of its parent list plus
+    // the true-dependency supplement; the edges walked at completion are the host child lists (as the
+    // reference walks child_ninst_arr, src/dse.c:372-375) plus the supplement.  For a generated graph the
+    // two agree; a file whose lists disagree yields a tile that never becomes ready, which the
+    // scheduler reports as a stall.
     const unsigned n = nasm->num_ninst;
     std::vector<TileDev> tiles(n);
     std::vector<std::vector<unsigned>> kids(n);
@@ -471,17 +475,21 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
         for (int pass = 0; pass < 2; pass++)
             for (unsigned par : (pass == 0 ? ni.parent_ninst_idx : ni.extra_parent_idx)) {
                 if (par >= n || par >= t) { ASPEN_ERR("tile %u lists parent %u that does not precede it\n", t, par); return -1; }
-                kids[par].push_back(t);
+                if (pass == 1) kids[par].push_back(t);
                 if (par < n_input) dep_init[t]++;
             }
+        for (unsigned child : ni.child_ninst_idx) {
+            if (child >= n || child <= t) { ASPEN_ERR("tile %u lists child %u that does not follow it\n", t, child); return -1; }
+            kids[t].push_back(child);
+        }
         if (t >= n_input && T.need == 0) { ASPEN_ERR("tile %u of layer %u has no parents and can never run\n", t, T.layer); return -1; }
         if (t >= n_input && dep_init[t] == T.need) init_ready.push_back(t);
     }
-    std::vector<unsigned> children;
+    std::vector<unsigned> children;   // pairs: (child tile, count that child waits for)
     for (unsigned t = 0; t < n; t++) {
-        tiles[t].child_off = (unsigned)children.size();
+        tiles[t].child_off = (unsigned)(children.size() / 2);
         tiles[t].child_cnt = (unsigned)kids[t].size();
-        children.insert(children.end(), kids[t].begin(), kids[t].end());
+        for (unsigned c : kids[t]) { children.push_back(c); children.push_back(tiles[c].need); }
     }
     for (unsigned i = 0; i < nasm->num_ldata; i++) layer_tiles[i] = nasm->ldata[i].num_ninst;
     std::vector<unsigned> zeros(std::max(n, nasm->num_ldata), 0);
@@ -614,9 +622,9 @@ static int launch_run(Engine *e, const std::vector<nasm_t *> &run) {
     sched::arm_kernel<<<arm_blocks, 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue, total, n_init, n_input, e->stall_ns, e->pipe_ns);
     sched::seed_kernel<<<std::max(1u, std::min<unsigned>((n_init + 255) / 256, 256)), 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue);
     if (e->precision == 0)
-        sched::scheduler_kernel<true><<<e->n_ctas, tc::NTHREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
+        sched::scheduler_kernel<true><<<e->n_ctas, sched::SCHED_THREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
     else
-        sched::scheduler_kernel<false><<<e->n_ctas, tc::NTHREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
+        sched::scheduler_kernel<false><<<e->n_ctas, sched::SCHED_THREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
     e->launches += 3;
     CUDA_TRY(cudaGetLastError());
     return 0;

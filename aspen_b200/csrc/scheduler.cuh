@@ -27,7 +27,7 @@
 namespace sched {
 
 constexpr unsigned PROF_LAYERS = 256;
-constexpr unsigned PROF_SLOTS = 2 + 2 * PROF_LAYERS;
+constexpr unsigned PROF_SLOTS = 2 + 2 * PROF_LAYERS + 2;
 
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
@@ -45,68 +45,27 @@ __device__ __forceinline__ unsigned ld_relaxed(const unsigned *p) {
     return v;
 }
 
-// Called by lane 0 of the control warp.  Returns a global tile id or ASPEN_TILE_NONE.
-__device__ unsigned pop_ready(CtrlDev *ctrl, const unsigned *queue, StatusHost *status) {
-    if (ld_relaxed(&ctrl->stop) || ld_relaxed(&ctrl->abort)) return ASPEN_TILE_NONE;
-    const unsigned ticket = atomicAdd(&ctrl->head, 1u);
-    const unsigned total = ctrl->total, cap = ctrl->cap;
-    if (ticket >= cap) return ASPEN_TILE_NONE;          // every tile that can ever be pushed already has an owner
-    unsigned last_done = ld_relaxed(&ctrl->done);
-    unsigned long long t_last = global_ns();
-    const unsigned long long window = ctrl->stall_ns;
-    for (unsigned spin = 0;; spin++) {
-        unsigned v = ld_acquire(&queue[ticket]);
-        if (v != 0u) return v - 1u;
-        unsigned done = ld_relaxed(&ctrl->done);
-        if (done >= total) return ASPEN_TILE_NONE;      // run finished; this ticket is never filled
-        if (ld_relaxed(&ctrl->abort) || ld_relaxed(&ctrl->stop)) return ASPEN_TILE_NONE;
-        if ((spin & 63u) == 63u) {
-            unsigned long long now = global_ns();
-            if (done != last_done) { last_done = done; t_last = now; }
-            else if (now - t_last > window) {
-                if (atomicCAS(&ctrl->abort, 0u, (unsigned)ASPEN_B200_ERR_STALL) == 0u) {
-                    status->info0 = ticket;
-                    status->info1 = done;
-                    status->status = ASPEN_B200_ERR_STALL;
-                    __threadfence_system();
-                }
-                return ASPEN_TILE_NONE;
-            }
-        }
-        __nanosleep(spin < 16u ? 32u : 256u);
-    }
-}
-
-// Called by the whole (converged) control warp after the tile's data is complete.
-// Returns the global id of a child this CTA should run next, or ASPEN_TILE_NONE.
-__device__ unsigned complete_tile(const NasmDev &G, unsigned local, CtrlDev *ctrl, unsigned *queue, StatusHost *status) {
+// Child update of a completed tile; called by the whole (converged) scheduler warp.  `children` holds
+// (child tile, count the child waits for) pairs so one load feeds both the atomic and the test.
+// Returns the global id of a child this CTA should run next (only when want_keep), or ASPEN_TILE_NONE.
+__device__ unsigned complete_children(const NasmDev &G, unsigned child_off, unsigned child_cnt, CtrlDev *ctrl, unsigned *queue, bool want_keep) {
     const unsigned lane = threadIdx.x & 31u;
-    const TileDev T = G.tiles[local];
+    const uint2 *edges = reinterpret_cast<const uint2 *>(G.children);
     __threadfence();                                     // release: this tile's output
-    if (lane == 0) {
-        unsigned d = atomicAdd(&G.layer_done[T.layer], 1u);
-        if (d + 1u == G.layer_tiles[T.layer]) {
-            unsigned l = atomicAdd(G.layers_completed, 1u);
-            if (l + 1u == G.n_layers) {
-                __threadfence_system();
-                *G.completed = 1u;                       // mapped host flag: the nasm is complete
-            }
-        }
-    }
     unsigned next = ASPEN_TILE_NONE;
-    for (unsigned base = 0; base < T.child_cnt; base += 32u) {
+    for (unsigned base = 0; base < child_cnt; base += 32u) {
         const unsigned idx = base + lane;
         unsigned child = ASPEN_TILE_NONE;
         bool ready = false;
-        if (idx < T.child_cnt) {
-            child = G.children[T.child_off + idx];
-            unsigned old = atomicAdd(&G.dep[child], 1u);
-            ready = old + 1u == G.tiles[child].need;
+        if (idx < child_cnt) {
+            const uint2 e = edges[child_off + idx];
+            child = e.x;
+            ready = atomicAdd(&G.dep[child], 1u) + 1u == e.y;
         }
         unsigned mask = __ballot_sync(0xffffffffu, ready);
         if (mask == 0u) continue;
         __threadfence();                                 // acquire the other parents' outputs (through the counters), then publish
-        if (next == ASPEN_TILE_NONE) {
+        if (want_keep && next == ASPEN_TILE_NONE) {
             const unsigned first = __ffs(mask) - 1u;
             next = __shfl_sync(0xffffffffu, child, first) + G.tile_base;
             mask &= ~(1u << first);
@@ -124,11 +83,23 @@ __device__ unsigned complete_tile(const NasmDev &G, unsigned local, CtrlDev *ctr
             }
         }
     }
-    if (lane == 0) {
-        unsigned d = atomicAdd(&ctrl->done, 1u);
-        if (((d + 1u) & 1023u) == 0u || d + 1u == ctrl->total) status->tiles_done = d + 1u;
+    return next;
+}
+
+// Completion accounting (ref src/dse.c:80-106): layer counter -> layers-completed counter -> the
+// graph's completed flag; run-wide tile count.  Not on the path of the next tile: done after it is posted.
+__device__ void complete_accounting(const NasmDev &G, unsigned layer, CtrlDev *ctrl, StatusHost *status) {
+    if ((threadIdx.x & 31u) != 0u) return;
+    unsigned d = atomicAdd(&G.layer_done[layer], 1u);
+    unsigned t = atomicAdd(&ctrl->done, 1u);
+    if (d + 1u == G.layer_tiles[layer]) {
+        unsigned l = atomicAdd(G.layers_completed, 1u);
+        if (l + 1u == G.n_layers) {
+            __threadfence_system();
+            *G.completed = 1u;                           // mapped host flag: the nasm is complete
+        }
     }
-    return __shfl_sync(0xffffffffu, next, 0);
+    if (((t + 1u) & 1023u) == 0u || t + 1u == ctrl->total) status->tiles_done = t + 1u;
 }
 
 // Resets the counters of every graph in the run and seeds the queue with the tiles that only
@@ -179,8 +150,150 @@ __device__ __forceinline__ void run_tile(const LayerDev &L, const TileDev &T, co
     }
 }
 
+// ---- the persistent kernel -------------------------------------------------------------------
+// Threads 0 .. tc::NTHREADS-1 are the EXECUTORS (worker warps, TMA thread, MMA thread): they run one tile
+// after the other out of a two-slot mailbox in shared memory.  The last warp is the SCHEDULER: when
+// the executors finish a tile it updates the children first (the first child that became ready is
+// posted straight back to the executors), and does the completion accounting and the queue
+// traffic while the executors already run the next tile.
+//   mailbox[k], k = sequence number & 1:  scheduler writes the tile id, arrives on posted[k];
+//   executors wait posted[k], run the tile, every executor thread arrives on finished[k];
+//   the scheduler waits finished[k] (so all stores of the tile are ordered before its gpu-scope
+//   fence and the counter updates), retires the tile and may then reuse slot k.
+constexpr unsigned SCHED_THREADS = tc::NTHREADS + 32u;
+
+// Executors' wait for the next tile.  The scheduler always posts an exit marker eventually (end of
+// run, stop, stall, abort); the time bound only guards against that logic failing.
+__device__ __forceinline__ bool wait_posted(unsigned long long *bar, unsigned parity, CtrlDev *ctrl, StatusHost *status) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns(), budget = 2ull * ctrl->stall_ns + 4ull * ctrl->pipe_ns + 1000000000ull;
+    for (unsigned spin = 1;; spin++) {
+        if (tc::mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 0u) {
+            __nanosleep(64);
+            if (global_ns() - t0 > budget) break;
+        }
+    }
+    if (atomicCAS(&ctrl->abort, 0u, (unsigned)ASPEN_B200_ERR_PIPE) == 0u) {
+        status->info0 = 7; status->info1 = blockIdx.x; status->status = ASPEN_B200_ERR_PIPE;
+        __threadfence_system();
+    }
+    return false;
+}
+
+__device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, CtrlDev *ctrl, unsigned *queue, StatusHost *status,
+                               tc::Shared *sh, unsigned long long *my_prof) {
+    const unsigned lane = threadIdx.x & 31u;
+    unsigned issued = 0, retired = 0;          // tiles posted to / retired from the mailbox
+    unsigned fl_nasm[2] = {0, 0}, fl_off[2] = {0, 0}, fl_cnt[2] = {0, 0}, fl_layer[2] = {0, 0};   // tiles in flight
+    unsigned acct_nasm = 0, acct_layer = ASPEN_TILE_NONE;   // completion accounting still to do
+    unsigned next = ASPEN_TILE_NONE;           // a ready tile waiting for a free slot
+    unsigned kept = ASPEN_TILE_NONE;           // a child made ready by a tile this CTA completed
+    unsigned ticket = ASPEN_TILE_NONE;         // a queue position we hold and wait on
+    bool closed = false;                        // no further tiles will be issued (end of run, stop, abort)
+    bool no_tickets = false;                    // the queue has no unowned position left; kept children still run
+    const unsigned total = ctrl->total, cap = ctrl->cap;
+    unsigned last_done = 0;
+    unsigned long long t_progress = __shfl_sync(0xffffffffu, global_ns(), 0), t_mark = t_progress;
+    const unsigned long long window = ctrl->stall_ns;
+    unsigned idle_spins = 0, turn = 0, flags = 0, done = 0;
+    while (true) {
+        bool progressed = false;
+        // control state is read by lane 0 and broadcast so the warp never diverges on it
+        // (global loads cost an L2 round trip each: while tiles are in flight they are sampled every 8th turn)
+        if (issued == retired || (turn++ & 7u) == 0u) {
+            unsigned f = 0, d = 0;
+            if (lane == 0) {
+                f = (ld_relaxed(&ctrl->abort) != 0u ? 1u : 0u) | (ld_relaxed(&ctrl->stop) != 0u ? 2u : 0u);
+                d = ld_relaxed(&ctrl->done);
+            }
+            flags = __shfl_sync(0xffffffffu, f, 0);
+            done = __shfl_sync(0xffffffffu, d, 0);
+        }
+        const bool halt = flags != 0u;
+        // 1. retire the oldest tile in flight once every executor thread has finished it
+        if (issued > retired) {
+            const unsigned k = retired & 1u;
+            unsigned ok = lane == 0 ? (unsigned)tc::mbar_test_wait(&sh->finished[k], (retired >> 1) & 1u) : 0u;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (ok) {
+                if (my_prof && lane == 0) t_mark = global_ns();
+                if (!(flags & 1u)) {
+                    unsigned child = complete_children(nasms[fl_nasm[k]], fl_off[k], fl_cnt[k], ctrl, queue, kept == ASPEN_TILE_NONE);
+                    if (child != ASPEN_TILE_NONE) kept = child;
+                    acct_nasm = fl_nasm[k]; acct_layer = fl_layer[k];
+                }
+                if (my_prof && lane == 0) my_prof[1] += global_ns() - t_mark;
+                retired++;
+                progressed = true;
+            }
+        }
+        // 2. find the next tile
+        if (halt) closed = true;
+        if (!closed && next == ASPEN_TILE_NONE) {
+            if (kept != ASPEN_TILE_NONE) { next = kept; kept = ASPEN_TILE_NONE; progressed = true; }
+            else {
+                // Only an idle CTA queues up for the next ready tile.  Claiming one while still busy was
+                // measured to cost 40 % of throughput: the claimed tile waits in this CTA's mailbox while
+                // other SMs that could have started it at once sit idle.
+                const bool take = ticket == ASPEN_TILE_NONE && !no_tickets && issued == retired;
+                if (take) {
+                    unsigned t = lane == 0 ? atomicAdd(&ctrl->head, 1u) : 0u;
+                    ticket = __shfl_sync(0xffffffffu, t, 0);
+                    if (ticket >= cap) { ticket = ASPEN_TILE_NONE; no_tickets = true; }   // every tile that can be pushed has an owner
+                }
+                if (ticket != ASPEN_TILE_NONE) {
+                    unsigned v = lane == 0 ? ld_acquire(&queue[ticket]) : 0u;
+                    v = __shfl_sync(0xffffffffu, v, 0);
+                    if (v != 0u) { next = v - 1u; ticket = ASPEN_TILE_NONE; progressed = true; }
+                }
+            }
+        }
+        // 3. post it when a mailbox slot is free
+        if (next != ASPEN_TILE_NONE && issued - retired < 2u) {
+            const unsigned k = issued & 1u;
+            if (lane == 0) { sh->mailbox[k] = next; tc::mbar_arrive(&sh->posted[k]); }
+            // remember what retiring this tile will need (loaded now, off the critical path)
+            unsigned g = 0;
+            while (g + 1u < n_nasm && next >= nasms[g + 1u].tile_base) g++;
+            const TileDev T = nasms[g].tiles[next - nasms[g].tile_base];
+            fl_nasm[k] = g; fl_off[k] = T.child_off; fl_cnt[k] = T.child_cnt; fl_layer[k] = T.layer;
+            issued++;
+            next = ASPEN_TILE_NONE;
+            progressed = true;
+        }
+        if (acct_layer != ASPEN_TILE_NONE) { complete_accounting(nasms[acct_nasm], acct_layer, ctrl, status); acct_layer = ASPEN_TILE_NONE; }
+        // 4. end of run / stall detection
+        if (done >= total) closed = true;
+        if (issued == retired) {
+            if (closed && (next == ASPEN_TILE_NONE || halt)) break;
+            if (no_tickets && next == ASPEN_TILE_NONE && kept == ASPEN_TILE_NONE && ticket == ASPEN_TILE_NONE) break;   // can never get work again
+        }
+        if (progressed || done != last_done) {
+            unsigned long long now = lane == 0 ? global_ns() : 0ull;
+            last_done = done; t_progress = __shfl_sync(0xffffffffu, now, 0); idle_spins = 0;
+            continue;
+        }
+        if (((++idle_spins) & 31u) == 0u) {
+            unsigned long long now = lane == 0 ? global_ns() : 0ull;
+            now = __shfl_sync(0xffffffffu, now, 0);
+            if (now - t_progress > window && issued == retired) {
+                // nothing running here, nothing completed anywhere for a whole window: the graph cannot progress
+                if (lane == 0 && atomicCAS(&ctrl->abort, 0u, (unsigned)ASPEN_B200_ERR_STALL) == 0u) {
+                    status->info0 = ticket; status->info1 = done; status->status = ASPEN_B200_ERR_STALL;
+                    __threadfence_system();
+                }
+                closed = true;
+            }
+            if (my_prof && lane == 0 && issued == retired) my_prof[0] += 1ull;   // idle polls with nothing in flight
+        }
+        __nanosleep(issued == retired ? 100u : 20u);
+    }
+    if (lane == 0) { sh->mailbox[issued & 1u] = ASPEN_TILE_NONE; tc::mbar_arrive(&sh->posted[issued & 1u]); }
+}
+
 template <bool TENSOR_CORES>
-__global__ void __launch_bounds__(tc::NTHREADS, 1)
+__global__ void __launch_bounds__(SCHED_THREADS, 1)
 scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHost *status, unsigned long long *prof) {
     extern __shared__ unsigned char smem_raw[];
     // stage buffers need 1024-byte alignment for the 128-byte swizzle
@@ -190,13 +303,14 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
     const unsigned ctrl_warp = tc::NW >> 5;
     tc::PipeState ps;
 
+    if (tid == 0) {
+        for (int s = 0; s < tc::STAGES; s++) { tc::mbar_init(&sh->full[s], tc::NW); tc::mbar_init(&sh->empty[s], 1u); tc::mbar_init(&sh->landed[s], 1u); }
+        tc::mbar_init(&sh->accum, 1u);
+        for (int k = 0; k < 2; k++) { tc::mbar_init(&sh->posted[k], 1u); tc::mbar_init(&sh->finished[k], tc::NTHREADS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        tc::fence_proxy_async_smem();
+    }
     if (TENSOR_CORES) {
-        if (tid == 0) {
-            for (int s = 0; s < tc::STAGES; s++) { tc::mbar_init(&sh->full[s], tc::NW); tc::mbar_init(&sh->empty[s], 1u); tc::mbar_init(&sh->landed[s], 1u); }
-            tc::mbar_init(&sh->accum, 1u);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            tc::fence_proxy_async_smem();
-        }
         if (warp == ctrl_warp + 1u) tc::tmem_alloc(&sh->tmem_base, tc::TMEM_COLS);
         tc::tc_fence_before();
     }
@@ -204,44 +318,38 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
     if (TENSOR_CORES) tc::tc_fence_after();
 
     const unsigned n_nasm = ctrl->n_nasm;
-    unsigned next = ASPEN_TILE_NONE;
-    // Optional time accounting (per CTA, by the control thread): [0] waiting for a ready tile,
-    // [1] completion + child update, [2 + layer] running tiles of that layer (index modulo PROF_LAYERS),
-    // [2 + PROF_LAYERS + layer] tile counts.
+    // Optional time accounting per CTA: [0] scheduler idle polls, [1] completion + child update (ns),
+    // [2 + layer] ns the executors spent on tiles of that layer (index modulo PROF_LAYERS),
+    // [2 + PROF_LAYERS + layer] tile counts, [PROF_SLOTS - 1] ns the executors waited for a tile.
     unsigned long long *my_prof = prof ? prof + (size_t)blockIdx.x * PROF_SLOTS : nullptr;
-    unsigned long long t_mark = my_prof ? global_ns() : 0ull;
-    while (true) {
-        if (tid == tc::TMA_THREAD) {
-            sh->tile = next != ASPEN_TILE_NONE ? next : pop_ready(ctrl, queue, status);
-            if (my_prof) { unsigned long long now = global_ns(); my_prof[0] += now - t_mark; t_mark = now; }
-        }
-        __syncthreads();
-        const unsigned gid = sh->tile;
-        if (gid == ASPEN_TILE_NONE) break;
-        unsigned g = 0;
-        while (g + 1u < n_nasm && gid >= nasms[g + 1u].tile_base) g++;
-        const NasmDev &G = nasms[g];
-        const unsigned local = gid - G.tile_base;
-        const TileDev T = G.tiles[local];
-        const LayerDev &L = G.layers[T.layer];
-        run_tile<TENSOR_CORES>(L, T, G, stage_mem, sh, ps, ctrl, status);
-        __syncthreads();                                  // every thread's stores of this tile are issued
-        if (warp == ctrl_warp) {
-            if (my_prof && tid == tc::TMA_THREAD) {
+
+    if (warp == (SCHED_THREADS >> 5) - 1u) {
+        scheduler_warp(nasms, n_nasm, ctrl, queue, status, sh, my_prof);
+    } else {
+        unsigned long long t_mark = my_prof ? global_ns() : 0ull;
+        for (unsigned seq = 0;; seq++) {
+            const unsigned k = seq & 1u;
+            if (!wait_posted(&sh->posted[k], (seq >> 1) & 1u, ctrl, status)) break;
+            const unsigned gid = sh->mailbox[k];
+            if (gid == ASPEN_TILE_NONE) break;
+            if (my_prof && tid == 0) { unsigned long long now = global_ns(); my_prof[PROF_SLOTS - 1] += now - t_mark; t_mark = now; }
+            unsigned g = 0;
+            while (g + 1u < n_nasm && gid >= nasms[g + 1u].tile_base) g++;
+            const NasmDev &G = nasms[g];
+            const TileDev T = G.tiles[gid - G.tile_base];
+            const LayerDev &L = G.layers[T.layer];
+            run_tile<TENSOR_CORES>(L, T, G, stage_mem, sh, ps, ctrl, status);
+            if (my_prof && tid == 0) {
                 unsigned long long now = global_ns();
                 my_prof[2 + T.layer % PROF_LAYERS] += now - t_mark; my_prof[2 + PROF_LAYERS + T.layer % PROF_LAYERS] += 1ull; t_mark = now;
             }
-            next = ASPEN_TILE_NONE;
-            if (!ps.dead && !sched::ld_relaxed(&ctrl->abort)) next = complete_tile(G, local, ctrl, queue, status);
-            if (my_prof && tid == tc::TMA_THREAD) { unsigned long long now = global_ns(); my_prof[1] += now - t_mark; t_mark = now; }
+            tc::mbar_arrive(&sh->finished[k]);             // release (CTA scope): this thread's stores of the tile
         }
     }
 
-    if (TENSOR_CORES) {
-        tc::tc_fence_before();
-        __syncthreads();
-        if (warp == ctrl_warp + 1u) { tc::tc_fence_after(); tc::tmem_dealloc(sh->tmem_base, tc::TMEM_COLS); }
-    }
+    if (TENSOR_CORES) tc::tc_fence_before();
+    __syncthreads();
+    if (TENSOR_CORES && warp == ctrl_warp + 1u) { tc::tc_fence_after(); tc::tmem_dealloc(sh->tmem_base, tc::TMEM_COLS); }
 }
 
 }  // namespace sched

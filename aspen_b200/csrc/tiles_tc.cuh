@@ -45,7 +45,9 @@ struct Shared {
     unsigned long long landed[STAGES];   // TMA bytes of a stage have arrived
     unsigned long long accum;
     unsigned tmem_base;
-    unsigned tile;            // scheduler mailbox
+    unsigned long long posted[2];     // scheduler -> executors: mailbox slot holds a tile
+    unsigned long long finished[2];   // executors -> scheduler: every executor thread is done with the slot's tile
+    unsigned mailbox[2];
     float partial[NW];        // K-attention row sums of the two column halves
 };
 
@@ -71,6 +73,14 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long *bar, u
 __device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned parity) {
     unsigned ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Non-blocking probe (try_wait may suspend the thread for a hardware-defined time; a polling loop
+// that has other things to look at uses this one).
+__device__ __forceinline__ bool mbar_test_wait(unsigned long long *bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
@@ -269,6 +279,10 @@ __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDev &G, u
     const void *amap = a_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.amap * 128) : nullptr;
     const void *bmap = b_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.wmap * 128) : nullptr;
     const bool vec_x = L.a_vec4 != 0;
+
+    // Activations were written with ordinary (generic proxy) stores, possibly by this very CTA a moment
+    // ago; TMA reads them through the async proxy.
+    if (tid == TMA_THREAD && a_tma) asm volatile("fence.proxy.async.global;" ::: "memory");
 
     for (unsigned n0 = 0; n0 < T.tile_w; n0 += 128) {
         const unsigned rows_valid = min(128u, T.tile_w - n0);

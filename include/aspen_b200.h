@@ -199,9 +199,10 @@ double aspen_b200_group_time_runs(dse_group_t *dse_group, unsigned int warmup, u
 
 /* Time accounting of the device scheduler (replaces the reference's wall-clock probes,
  * ref src/util.c:490-539).  Active when the environment variable ASPEN_B200_PROFILE is set before
- * dse_group_init.  out[514], nanoseconds summed over all worker CTAs since the last call:
- * [0] waiting for a ready tile, [1] completion and child update, [2 + l] running tiles of layer l
- * (l modulo 256), [258 + l] number of tiles of layer l.  Returns 0, or -1 when inactive. */
+ * dse_group_init.  out[516], summed over all worker CTAs since the last call: [0] scheduler polls
+ * made with nothing in flight, [1] ns spent on completion and child updates, [2 + l] ns the executor
+ * warps spent on tiles of layer l (l modulo 256), [258 + l] number of tiles of layer l, [515] ns the
+ * executor warps waited for a tile.  Returns 0, or -1 when inactive. */
 int aspen_b200_group_profile(dse_group_t *dse_group, unsigned long long *out, unsigned int *n_ctas);
 
 #ifdef __cplusplus
