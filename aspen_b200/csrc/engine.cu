@@ -288,11 +288,11 @@ static int ensure_xfer(Engine *e, size_t bytes) {
 }
 
 // packed [W][H] <-> strided [W][ld] activation matrix
-__global__ void unpack_columns(float *dst, const float *src, unsigned H, unsigned ld, size_t n) {
+__global__ void unpack_columns(float *dst, const float *src, unsigned H, unsigned ld, size_t n, int round) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         size_t w = i / H;
         unsigned h = (unsigned)(i - w * H);
-        dst[w * ld + h] = src[i];
+        dst[w * ld + h] = round ? tf32_round(src[i]) : src[i];
     }
 }
 __global__ void round_tf32_inplace(float *p, size_t n) {
@@ -530,13 +530,12 @@ int engine_set_input(nasm_t *nasm, const void *input_host) {
         if (ensure_xfer(e, n * sizeof(float)) != 0) return -1;
         CUDA_TRY(cudaMemcpyAsync(e->xfer, input_host, n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
         unsigned blocks = (unsigned)std::min<size_t>((n + 255) / 256, 4096);
-        unpack_columns<<<blocks, 256, 0, e->stream>>>(dst, e->xfer, l0.out_mat_dims[OUT_H], l0.out_mat_stride, n);
+        unpack_columns<<<blocks, 256, 0, e->stream>>>(dst, e->xfer, l0.out_mat_dims[OUT_H], l0.out_mat_stride, n, dn->round_input ? 1 : 0);
         e->launches++;
         CUDA_TRY(cudaGetLastError());
     }
-    if (dn->round_input) {
-        size_t total = l0.out_mat_mem_size / sizeof(float);
-        round_tf32_inplace<<<(unsigned)std::min<size_t>((total + 255) / 256, 4096), 256, 0, e->stream>>>(dst, total);
+    if (dn->round_input && l0.out_mat_stride == l0.out_mat_dims[OUT_H]) {   // packed layout: round in place (the strided path rounds while scattering)
+        round_tf32_inplace<<<(unsigned)std::min<size_t>((n + 255) / 256, 4096), 256, 0, e->stream>>>(dst, n);
         e->launches++;
     }
     // The caller may reuse its buffer as soon as we return (the reference copies synchronously).

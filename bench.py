@@ -34,8 +34,10 @@ WORKLOADS = {
     "resnet50": ("resnet50", 32, 0, "he", 1, 0),
     "bert_base": ("bert_base", 32, 128, "n002", 3, 3),
 }
+# DRAM bytes per scheduler launch, from the ncu capture summarised in profiles/ (batch-4 case scaled by 8).
+TRAFFIC_BYTES = {"resnet50": 2.4e9}
 MIN_NINST = 296          # at least two tiles per SM and layer
-TILE_PROFILE = 1         # 64-row x 128-column quanta (tensor-core shaped); values do not depend on it
+TILE_PROFILE = 1         # 128-row x 128-column quanta (tensor-core shaped); values do not depend on it
 
 
 def log(*a):
@@ -280,7 +282,7 @@ def report(args, world, workload, batch, seq, nasm, flops, arena_bytes, ms, max_
         "metric": "inferences_per_sec", "value": value, "unit": "inf/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": max_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32",
         "data": "synthetic",
-        "config": {"workload": f"{workload}_bs{batch}_per_gpu", "seq_len": seq or None, "tile_profile": "b200 64x128",
+        "config": {"workload": f"{workload}_bs{batch}_per_gpu", "seq_len": seq or None, "tile_profile": "b200 128x128",
                    "min_ninst_per_ldata": MIN_NINST, "tiles": nasm.num_ninst, "flops_per_step": flops,
                    "l2": f"no flush: each step streams a {arena_bytes / 1e9:.2f} GB activation arena (> 126 MB L2)"},
         "clocks": clocks,
@@ -288,7 +290,7 @@ def report(args, world, workload, batch, seq, nasm, flops, arena_bytes, ms, max_
                 "d2h_bytes_per_step": int(out.nbytes), "ms_per_step": e2e_max / args.steps},
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
-                     "traffic": None, "peak_source": peak_src,
+                     "traffic": TRAFFIC_BYTES.get(workload), "peak_source": peak_src,
                      "note": "kernel = persistent scheduler_kernel<true> (whole tile graph, all layer types); operands are TF32, whose dense "
                              "peak is half the bf16 figure used as denominator"},
     }
