@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libaspen_b200.so")
-SOURCES = ["cfg.cpp", "dnn.cpp", "tiler.cpp", "graph.cpp", "runtime.cpp", "engine.cu"]
+SOURCES = ["cfg.cpp", "dnn.cpp", "tiler.cpp", "graph.cpp", "runtime.cpp", "engine.cu", "noalloc.cu"]
 HEADERS = ["internal.h", "device_types.h", "tiles_simt.cuh", "tiles_tc.cuh", "scheduler.cuh",
            os.path.join("..", "..", "include", "aspen_b200.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

@@ -48,7 +48,7 @@ __device__ __forceinline__ unsigned ld_relaxed(const unsigned *p) {
 // Child update of a completed tile; called by the whole (converged) scheduler warp.  `children` holds
 // (child tile, count the child waits for) pairs so one load feeds both the atomic and the test.
 // Returns the global id of a child this CTA should run next (only when want_keep), or ASPEN_TILE_NONE.
-__device__ unsigned complete_children(const NasmDev &G, unsigned child_off, unsigned child_cnt, CtrlDev *ctrl, unsigned *queue, bool want_keep) {
+static __device__ unsigned complete_children(const NasmDev &G, unsigned child_off, unsigned child_cnt, CtrlDev *ctrl, unsigned *queue, bool want_keep) {
     const unsigned lane = threadIdx.x & 31u;
     const uint2 *edges = reinterpret_cast<const uint2 *>(G.children);
     __threadfence();                                     // release: this tile's output
@@ -88,7 +88,7 @@ __device__ unsigned complete_children(const NasmDev &G, unsigned child_off, unsi
 
 // Completion accounting (ref src/dse.c:80-106): layer counter -> layers-completed counter -> the
 // graph's completed flag; run-wide tile count.  Not on the path of the next tile: done after it is posted.
-__device__ void complete_accounting(const NasmDev &G, unsigned layer, CtrlDev *ctrl, StatusHost *status) {
+static __device__ void complete_accounting(const NasmDev &G, unsigned layer, CtrlDev *ctrl, StatusHost *status) {
     if ((threadIdx.x & 31u) != 0u) return;
     unsigned d = atomicAdd(&G.layer_done[layer], 1u);
     unsigned t = atomicAdd(&ctrl->done, 1u);
@@ -104,7 +104,7 @@ __device__ void complete_accounting(const NasmDev &G, unsigned layer, CtrlDev *c
 
 // Resets the counters of every graph in the run and seeds the queue with the tiles that only
 // depend on input tiles (push_first_layer_to_rpool, ref src/dse.c:443-470).
-__global__ void arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, unsigned total, unsigned n_init_total,
+static __global__ void arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, unsigned total, unsigned n_init_total,
                            unsigned n_input_total, unsigned long long stall_ns, unsigned long long pipe_ns) {
     const unsigned stride = gridDim.x * blockDim.x, t0 = blockIdx.x * blockDim.x + threadIdx.x;
     const unsigned n_nasm = ctrl->n_nasm;
@@ -122,7 +122,7 @@ __global__ void arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, unsig
     }
 }
 // Second step of arming (after every slot was cleared): write the initial ready tiles.
-__global__ void seed_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue) {
+static __global__ void seed_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue) {
     const unsigned stride = gridDim.x * blockDim.x, t0 = blockIdx.x * blockDim.x + threadIdx.x;
     for (unsigned g = 0; g < ctrl->n_nasm; g++) {
         const NasmDev G = nasms[g];
@@ -181,7 +181,7 @@ __device__ __forceinline__ bool wait_posted(unsigned long long *bar, unsigned pa
     return false;
 }
 
-__device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, CtrlDev *ctrl, unsigned *queue, StatusHost *status,
+static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, CtrlDev *ctrl, unsigned *queue, StatusHost *status,
                                tc::Shared *sh, unsigned long long *my_prof) {
     const unsigned lane = threadIdx.x & 31u;
     unsigned issued = 0, retired = 0;          // tiles posted to / retired from the mailbox

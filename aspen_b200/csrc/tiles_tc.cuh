@@ -265,7 +265,7 @@ __device__ __forceinline__ Operands make_operands(const LayerDev &L, const TileD
 }
 
 // One ninst tile.  Called by all NTHREADS threads of the CTA.
-__device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDev &G, unsigned char *stage_mem, Shared *sh,
+static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDev &G, unsigned char *stage_mem, Shared *sh,
                           PipeState &ps, CtrlDev *ctrl, StatusHost *status) {
     const unsigned tid = threadIdx.x;
     const bool is_worker = tid < NW;

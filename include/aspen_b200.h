@@ -205,6 +205,29 @@ double aspen_b200_group_time_runs(dse_group_t *dse_group, unsigned int warmup, u
  * executor warps waited for a tile.  Returns 0, or -1 when inactive. */
 int aspen_b200_group_profile(dse_group_t *dse_group, unsigned long long *out, unsigned int *n_ctas);
 
+/* No counterpart in the reference.  One matmul layer, out[n][m] = act(bias[m] + sum_k w[m][k] * x[n][k])
+ * in fp32 FMA arithmetic, run as 128 x 128 tiles by the same persistent scheduler kernel as every
+ * other call -- but WITHOUT ALLOCATING ANYTHING.  It is for callers that are not allowed to call
+ * cudaMalloc: code running inside another party's stream capture, plug-ins of a serving runtime that
+ * fixes all memory pools at start-up, loops that cannot afford the device-wide synchronisation an
+ * allocation implies.  All pointers are DEVICE pointers the caller owns: x [n_cols][k], w [m][k],
+ * bias [m] or NULL, out [n_cols][m], rows contiguous; cuda_stream is a cudaStream_t (NULL = default).
+ * Everything else the scheduler needs (tile descriptors, ready queue, counters, status) lives in one
+ * fixed array in device memory that every GPU holds from the moment the library is loaded until exit
+ * (about 180 KB).  Hence:
+ *   - at most ASPEN_B200_NOALLOC_MAX_TILES tiles, i.e. ceil(m/128) * ceil(n_cols/128) <= 4096; a larger
+ *     call fails with -2 and changes nothing;
+ *   - all calls on one GPU share the array, which still holds the previous call's data: each call
+ *     rewrites what it reads (counters and queue start from zero), and calls that overlap on the GPU
+ *     -- two streams, two host threads -- corrupt each other.  Serialise them;
+ *   - the first call on a device resolves the array's device address; make that call before any
+ *     stream capture begins.
+ * The call returns after the work has finished.  Returns 0, -1 bad arguments, -2 too large, -3 CUDA
+ * error, -4 the scheduler reported an error (see aspen_b200_last_error). */
+#define ASPEN_B200_NOALLOC_MAX_TILES 4096
+int aspen_b200_matmul_noalloc(const float *x_dev, const float *w_dev, const float *bias_dev, float *out_dev,
+                              unsigned int n_cols, unsigned int k, unsigned int m, int activation, void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
