@@ -26,6 +26,13 @@ struct LayerDev {
     unsigned a_kind, b_kind;  // operand staging, see tiles_tc.cuh
     unsigned a_vec4;          // activation rows can be fetched in 16-byte pieces (IC % 4 == 0 ...)
     unsigned round_out;       // store outputs rounded to TF32 (nearest): a tensor-core layer reads them
+    // A residual layer fused into this (convolution / matmul) layer's epilogue: besides its own output the tile
+    // also writes res_out = act(own + res_in) for the same region.  res_out == nullptr: nothing fused.
+    const float *res_in;
+    float *res_out;
+    unsigned res_ld_in, res_ld_out;
+    int res_act;
+    unsigned res_round;
 };
 
 struct TileDev {
@@ -34,7 +41,12 @@ struct TileDev {
     unsigned tile_h, tile_w;  // clipped extents
     unsigned child_off, child_cnt;
     unsigned need;            // number of parent tiles (true dependencies)
+    unsigned flags;           // TILE_WRITTEN_BY_PARENTS
 };
+
+// The tile's values were already written by the tiles it depends on (a residual layer fused into its
+// producer): the scheduler completes it as soon as it is ready, no executor runs it.
+#define TILE_WRITTEN_BY_PARENTS 1u
 
 struct NasmDev {
     const LayerDev *layers;

@@ -448,6 +448,33 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
         }
     }
     dn->round_input = layers[0].round_out != 0;
+    // Residual fusion (tensor-core path): a residual layer whose later parent is a convolution or a matmul
+    // is computed in that parent's epilogue, which then needs the earlier parent's tiles of the same region
+    // (fused_other[producer] = that layer).  The residual layer's own tiles stay in the graph and only pass
+    // completion on.  ASPEN_B200_NO_FUSE=1 keeps the layers separate.
+    std::vector<unsigned> fused_other(nasm->num_ldata, (unsigned)-1);
+    std::vector<unsigned char> written_by_parents(nasm->num_ldata, 0);
+    const char *no_fuse = getenv("ASPEN_B200_NO_FUSE");
+    if (e->precision == 0 && !(no_fuse && atoi(no_fuse) != 0)) {
+        for (unsigned i = 1; i < nasm->num_ldata; i++) {
+            if (nasm->ldata[i].layer->type != RESIDUAL_LAYER) continue;
+            const unsigned a = nasm->ldata[i].parent_ldata_idx_arr[PARENT_0], b = nasm->ldata[i].parent_ldata_idx_arr[PARENT_1];
+            if (a == (unsigned)-1 || b == (unsigned)-1 || a == b) continue;
+            const unsigned hi = std::max(a, b), lo = std::min(a, b);
+            const LAYER_TYPE t = nasm->ldata[hi].layer->type;
+            if (lo == 0 || (t != CONV_LAYER && t != MATMUL_LAYER) || layers[hi].res_out) continue;
+            const nasm_ldata_t &R = nasm->ldata[i], &P = nasm->ldata[hi], &Q = nasm->ldata[lo];
+            if (P.out_mat_dims[OUT_H] != R.out_mat_dims[OUT_H] || P.out_mat_dims[OUT_W] != R.out_mat_dims[OUT_W] ||
+                Q.out_mat_dims[OUT_H] != R.out_mat_dims[OUT_H] || Q.out_mat_dims[OUT_W] != R.out_mat_dims[OUT_W])
+                continue;
+            LayerDev &L = layers[hi];
+            L.res_in = layers[lo].out; L.res_ld_in = layers[lo].ldc;
+            L.res_out = layers[i].out; L.res_ld_out = layers[i].ldc;
+            L.res_act = layers[i].act; L.res_round = layers[i].round_out;
+            fused_other[hi] = lo;
+            written_by_parents[i] = 1;
+        }
+    }
     if (to_device(&dn->layers, layers) != 0) return -1;
     {
         size_t bytes = std::max<size_t>(maps.size(), 1) * sizeof(CUtensorMap);
@@ -472,6 +499,22 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
         T.pos_h = ni.out_mat_pos[OUT_H]; T.pos_w = ni.out_mat_pos[OUT_W];
         T.tile_h = ni.tile_dims[OUT_H]; T.tile_w = ni.tile_dims[OUT_W];
         T.need = (unsigned)(ni.parent_ninst_idx.size() + ni.extra_parent_idx.size());
+        T.flags = written_by_parents[T.layer] ? TILE_WRITTEN_BY_PARENTS : 0u;
+        if (fused_other[T.layer] != (unsigned)-1) {
+            // the fused residual reads the other parent over this tile's own region: tiles of that layer's grid
+            // (rows fastest) that overlap it become parents too
+            const nasm_ldata_t &Q = nasm->ldata[fused_other[T.layer]];
+            const unsigned qh = Q.ninst_tile_dims[OUT_H], qw = Q.ninst_tile_dims[OUT_W];
+            const unsigned per_col = (Q.out_mat_dims[OUT_H] + qh - 1) / qh;
+            for (unsigned cw = T.pos_w / qw; cw <= (T.pos_w + T.tile_w - 1) / qw; cw++)
+                for (unsigned ch = T.pos_h / qh; ch <= (T.pos_h + T.tile_h - 1) / qh; ch++) {
+                    const unsigned par = Q.ninst_start + cw * per_col + ch;
+                    if (par >= Q.ninst_start + Q.num_ninst || par >= t) { ASPEN_ERR("fused residual: tile %u has no valid producer tile\n", t); return -1; }
+                    kids[par].push_back(t);
+                    T.need++;
+                    if (par < n_input) dep_init[t]++;
+                }
+        }
         for (int pass = 0; pass < 2; pass++)
             for (unsigned par : (pass == 0 ? ni.parent_ninst_idx : ni.extra_parent_idx)) {
                 if (par >= n || par >= t) { ASPEN_ERR("tile %u lists parent %u that does not precede it\n", t, par); return -1; }

@@ -63,7 +63,7 @@ __global__ void noalloc_setup(NoAllocScratch *s, NoAllocArgs a) {
         T.pos_w = (t / tiles_h) * NOALLOC_TILE;
         T.tile_h = min(NOALLOC_TILE, a.m - T.pos_h);
         T.tile_w = min(NOALLOC_TILE, a.n_cols - T.pos_w);
-        T.child_off = 0; T.child_cnt = 0; T.need = 0;
+        T.child_off = 0; T.child_cnt = 0; T.need = 0; T.flags = 0;
         s->tiles[t] = T;
         s->queue[t] = t + 1u;
         s->dep[t] = 0u;

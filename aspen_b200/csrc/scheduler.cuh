@@ -251,14 +251,23 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
         }
         // 3. post it when a mailbox slot is free
         if (next != ASPEN_TILE_NONE && issued - retired < 2u) {
-            const unsigned k = issued & 1u;
-            if (lane == 0) { sh->mailbox[k] = next; tc::mbar_arrive(&sh->posted[k]); }
-            // remember what retiring this tile will need (loaded now, off the critical path)
             unsigned g = 0;
             while (g + 1u < n_nasm && next >= nasms[g + 1u].tile_base) g++;
             const TileDev T = nasms[g].tiles[next - nasms[g].tile_base];
-            fl_nasm[k] = g; fl_off[k] = T.child_off; fl_cnt[k] = T.child_cnt; fl_layer[k] = T.layer;
-            issued++;
+            if (T.flags & TILE_WRITTEN_BY_PARENTS) {
+                // nothing to execute: the tiles it waited for wrote its values; it completes right here
+                if (!(flags & 1u)) {
+                    unsigned child = complete_children(nasms[g], T.child_off, T.child_cnt, ctrl, queue, kept == ASPEN_TILE_NONE);
+                    if (child != ASPEN_TILE_NONE) kept = child;
+                    complete_accounting(nasms[g], T.layer, ctrl, status);
+                }
+            } else {
+                const unsigned k = issued & 1u;
+                if (lane == 0) { sh->mailbox[k] = next; tc::mbar_arrive(&sh->posted[k]); }
+                // remember what retiring this tile will need (loaded now, off the critical path)
+                fl_nasm[k] = g; fl_off[k] = T.child_off; fl_cnt[k] = T.child_cnt; fl_layer[k] = T.layer;
+                issued++;
+            }
             next = ASPEN_TILE_NONE;
             progressed = true;
         }

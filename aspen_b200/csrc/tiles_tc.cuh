@@ -199,6 +199,54 @@ __device__ __forceinline__ void store_block_coalesced(float *stage /*warp's 4 KB
     __syncwarp();
 }
 
+// Same block store, plus the fused residual layer (ref src/tiled_kernels.c:503-541 computes it as a layer
+// of its own): out2 = act(value + in2) for the same 32 x 32 block, read and written in the coalesced
+// layout.  The eight loads of in2 are issued before the first store so they overlap.
+__device__ __forceinline__ void store_block_residual(float *stage, const float *v, float *out_block, size_t ldc, unsigned n_valid,
+                                                     unsigned m_valid, const float *in2_block, size_t ld_in2, float *out2_block,
+                                                     size_t ld_out2, int act2, bool round2) {
+    const unsigned lane = threadIdx.x & 31u;
+    float4 *st = reinterpret_cast<float4 *>(stage);
+    #pragma unroll
+    for (unsigned j = 0; j < 8; j++) st[lane * 8u + (j ^ (lane & 7u))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    __syncwarp();
+    const unsigned piece = lane & 7u, m = piece * 4u;
+    const bool full = m + 4u <= m_valid;
+    float4 r[8];
+    #pragma unroll
+    for (unsigned i = 0; i < 8; i++) {
+        const unsigned n = i * 4u + (lane >> 3);
+        r[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (n < n_valid) {
+            const float *src = in2_block + (size_t)n * ld_in2 + m;
+            if (full) r[i] = ldcg4(src);
+            else {
+                if (m < m_valid) r[i].x = ldcg1(src);
+                if (m + 1u < m_valid) r[i].y = ldcg1(src + 1);
+                if (m + 2u < m_valid) r[i].z = ldcg1(src + 2);
+            }
+        }
+    }
+    #pragma unroll
+    for (unsigned i = 0; i < 8; i++) {
+        const unsigned n = i * 4u + (lane >> 3);
+        const float4 val = st[n * 8u + (piece ^ (n & 7u))];
+        float4 o = make_float4(activate(val.x + r[i].x, act2), activate(val.y + r[i].y, act2), activate(val.z + r[i].z, act2),
+                               activate(val.w + r[i].w, act2));
+        if (round2) o = make_float4(tf32_round(o.x), tf32_round(o.y), tf32_round(o.z), tf32_round(o.w));
+        if (n < n_valid) {
+            float *dst = out_block + (size_t)n * ldc + m, *dst2 = out2_block + (size_t)n * ld_out2 + m;
+            if (full) { *reinterpret_cast<float4 *>(dst) = val; *reinterpret_cast<float4 *>(dst2) = o; }
+            else {
+                if (m < m_valid) { dst[0] = val.x; dst2[0] = o.x; }
+                if (m + 1u < m_valid) { dst[1] = val.y; dst2[1] = o.y; }
+                if (m + 2u < m_valid) { dst[2] = val.z; dst2[2] = o.z; }
+            }
+        }
+    }
+    __syncwarp();
+}
+
 // ---- per-layer operand description -------------------------------------------------------------
 // How the two operands of a layer reach shared memory (chosen on the host, LayerDev::a_kind / b_kind):
 //   X side  A_GATHER     worker threads, cp.async per 16-byte piece (4-byte pieces when IC % 4 != 0): strided
@@ -502,7 +550,13 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                             #pragma unroll
                             for (unsigned j = 0; j < 32; j++) v[j] = tf32_round(v[j]);
                         }
-                        if (!ps.dead) store_block_coalesced(epi, v, oblk + c * 32u, L.ldc, n_valid, valid);
+                        if (!ps.dead) {
+                            if (L.res_out) {
+                                const size_t col0 = T.pos_w + n0 + lane_base, m0 = T.pos_h + ms + c * 32u;
+                                store_block_residual(epi, v, oblk + c * 32u, L.ldc, n_valid, valid, L.res_in + col0 * L.res_ld_in + m0, L.res_ld_in,
+                                                     L.res_out + col0 * L.res_ld_out + m0, L.res_ld_out, L.res_act, L.res_round != 0);
+                            } else store_block_coalesced(epi, v, oblk + c * 32u, L.ldc, n_valid, valid);
+                        }
                     }
                 }
                 tc_fence_before();

@@ -245,3 +245,23 @@ def test_stop_then_run_again_completes(workdir):
     assert dev.rerun() == 0
     np.testing.assert_array_equal(a, dev.nasm.ldata(dev.nasm.num_ldata - 1))
     dev.close()
+
+
+@pytest.mark.parametrize("name,batch,seq,mn,profile", [("resnet50", 2, 0, 100, 1), ("resnet50", 1, 0, 50, 0), ("tiny_transformer", 3, 24, 20, 0),
+                                                       ("bert_base", 2, 128, 100, 1)])
+def test_residual_fused_into_producer_equals_separate_layer(name, batch, seq, mn, profile, workdir, monkeypatch):
+    """The residual layers computed in the producing convolution / matmul epilogue (the default) give,
+    bit for bit, what the separate residual tiles (ref src/tiled_kernels.c:503-541) give, in every layer."""
+    cfg, wf = harness.prepare(name, workdir)
+    outs = []
+    for no_fuse in ("0", "1"):
+        monkeypatch.setenv("ASPEN_B200_NO_FUSE", no_fuse)
+        dev = harness.Device(cfg, wf, batch, seq, mn, 0, profile)
+        x = harness.make_input(name, dev.input_shape())
+        assert dev.run(x) == 0
+        outs.append([dev.nasm.ldata(i).copy() for i in range(1, dev.nasm.num_ldata)])
+        types = [api.LAYER_TYPES[dev.nasm.ldata_info(i)["type"]] for i in range(1, dev.nasm.num_ldata)]
+        dev.close()
+    assert "RESIDUAL" in types
+    for i, (a, b) in enumerate(zip(*outs)):
+        assert np.array_equal(a, b), f"layer {i + 1} ({types[i]}) differs"
