@@ -62,7 +62,7 @@ __device__ __forceinline__ const float *input_pixel(const LayerDev &L, const Pix
 
 // ref src/tiled_kernels.c:613-638.  Pure streaming (12 bytes per element): four independent 16-byte
 // load pairs are in flight per thread before the first use.
-static __device__ void tile_residual(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
+static __device__ __noinline__ void tile_residual(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
     const unsigned h4 = T.tile_h >> 2, tail = T.tile_h & 3;
     const unsigned total = T.tile_w * h4;
     constexpr int U = 4;
@@ -101,7 +101,7 @@ static __device__ void tile_residual(const LayerDev L, const TileDev T, unsigned
 // ref src/tiled_kernels.c:411-501.  Max ignores padded taps (all padded -> -inf); average divides by
 // the full window size, padding counted.
 template <bool IS_MAX>
-static __device__ void tile_pool(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
+static __device__ __noinline__ void tile_pool(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
     const unsigned h4 = T.tile_h >> 2, per_col = h4 + (T.tile_h & 3);
     const float inv = 1.f / (float)(L.KH * L.KW);
     for (unsigned i = tid; i < T.tile_w * per_col; i += nthr) {
@@ -142,7 +142,7 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // ref src/tiled_kernels.c:743-783: one pass mean / E[x^2], eps 1e-6, gain and shift.  One warp per column.
-static __device__ void tile_layernorm(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
+static __device__ __noinline__ void tile_layernorm(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
     const unsigned warp = tid >> 5, lane = tid & 31, nwarp = nthr >> 5;
     const unsigned M = T.tile_h;
     const float *gain = L.weight + T.pos_h;
@@ -180,7 +180,7 @@ static __device__ void tile_layernorm(const LayerDev L, const TileDev T, unsigne
 }
 
 // ref src/tiled_kernels.c:640-673: max-subtracted softmax down each column.  One warp per column.
-static __device__ void tile_softmax(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
+static __device__ __noinline__ void tile_softmax(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
     const unsigned warp = tid >> 5, lane = tid & 31, nwarp = nthr >> 5;
     const unsigned M = T.tile_h;
     for (unsigned n = warp; n < T.tile_w; n += nwarp) {
@@ -197,7 +197,7 @@ static __device__ void tile_softmax(const LayerDev L, const TileDev T, unsigned 
 }
 
 // ref src/tiled_kernels.c:675-709: box decode of one detection head.
-static __device__ void tile_yolo(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
+static __device__ __noinline__ void tile_yolo(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
     const unsigned C = L.p_out_c;
     const unsigned a_num = L.p_in_c / C, hw = L.IH * L.IW;
     for (unsigned i = tid; i < T.tile_w * C; i += nthr) {
@@ -220,7 +220,7 @@ static __device__ void tile_yolo(const LayerDev L, const TileDev T, unsigned tid
 }
 
 // ref src/tiled_kernels.c:711-741: nearest-neighbour upsample of PARENT_0 concatenated with PARENT_1.
-static __device__ void tile_append(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
+static __device__ __noinline__ void tile_append(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
     const unsigned c1 = L.p_in_c, c2 = L.p_out_c - L.p_in_c, C = c1 + c2;
     const unsigned w2 = L.OW, w1 = L.IW, s = L.p_stride;
     for (unsigned i = tid; i < T.tile_w * C; i += nthr) {
