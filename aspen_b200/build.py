@@ -19,7 +19,7 @@ HEADERS = ["internal.h", "device_types.h", "tiles_simt.cuh", "tiles_tc.cuh", "sc
            os.path.join("..", "..", "include", "aspen_b200.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
-         "-Xcompiler", "-Wall", "-Xcompiler", "-Wno-unused-function", "-cudart", "static"]
+         "-Xcompiler", "-Wall", "-Xcompiler", "-Wno-unused-function", "-cudart", "static"] + os.environ.get("ASPEN_B200_NVCC_FLAGS", "").split()
 
 
 def _stale() -> bool:

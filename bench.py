@@ -35,9 +35,11 @@ WORKLOADS = {
     "bert_base": ("bert_base", 32, 128, "n002", 3, 3),
 }
 # DRAM bytes per scheduler launch, from the ncu capture summarised in profiles/ (batch-4 case scaled by 8).
-TRAFFIC_BYTES = {"resnet50": 2.4e9}
-MIN_NINST = 296          # at least two tiles per SM and layer
-TILE_PROFILE = 1         # 128-row x 128-column quanta (tensor-core shaped); values do not depend on it
+TRAFFIC_BYTES = {"resnet50": 2.5e9}
+# Tiling of the nasm per workload: (row quantum, column quantum, min_ninst_per_ldata).  Tensor-core shaped
+# quanta; the values a graph computes do not depend on them.  Each is the best of a measured sweep
+# (quanta 64-256, min_ninst 100-592).
+TILING = {"resnet50": (128, 128, 148), "bert_base": (256, 128, 296)}
 
 
 def log(*a):
@@ -125,6 +127,24 @@ def job_value(units_per_rank: int, steps: int, world: int, max_ms: float) -> flo
     return units_per_rank * steps * world / (max_ms * 1e-3)
 
 
+class _StdoutToStderr:
+    """The reference library prints progress with printf; the bench line must be the only thing on stdout."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+
+    def __exit__(self, *exc):
+        try:
+            import ctypes
+            ctypes.CDLL(None).fflush(None)
+        except Exception:  # noqa: BLE001
+            pass
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+
+
 def cpu_reference_rate(workload: str, cfg: str, wfile: str, batch: int, steps: int, warmup: int, workdir: str):
     """Times the reference's own DSE path (main.c:116-123 loop) on the host cores.  The graph file is
     written by this library and loaded by the reference (identical graphs; the reference's own
@@ -140,11 +160,12 @@ def cpu_reference_rate(workload: str, cfg: str, wfile: str, batch: int, steps: i
     nasm.save(nfile)
     nasm.close()
     dnn.close()
-    rn = ref.RefNet(cfg, wfile, batch, seq, nasm_file=nfile)
-    i0 = rn.ldata_info(0)
-    x = np.random.default_rng(0).standard_normal((i0["W"], i0["H"]), dtype=np.float32)
-    sec = rn.bench_dse(x, cores, warmup, steps)
-    rn.close()
+    with _StdoutToStderr():
+        rn = ref.RefNet(cfg, wfile, batch, seq, nasm_file=nfile)
+        i0 = rn.ldata_info(0)
+        x = np.random.default_rng(0).standard_normal((i0["W"], i0["H"]), dtype=np.float32)
+        sec = rn.bench_dse(x, cores, warmup, steps)
+        rn.close()
     return batch / sec, cores
 
 
@@ -214,9 +235,10 @@ def main():
     wd = tempfile.mkdtemp(prefix=f"aspen_bench_r{rank}_")
     cfg, wfile = prepare_files(workload, wd)
 
-    L.aspen_b200_set_tile_profile(TILE_PROFILE)
+    q_h, q_w, min_ninst = TILING[workload]
+    L.aspen_b200_set_tile_quanta(q_h, q_w, 100000000)
     dnn = api.Dnn(cfg, wfile)
-    nasm = api.Nasm(dnn, batch, seq, MIN_NINST)
+    nasm = api.Nasm(dnn, batch, seq, min_ninst)
     L.aspen_b200_set_tile_profile(0)
     rpool = api.Rpool()
     group = api.DseGroup(0, 0)
@@ -282,8 +304,8 @@ def report(args, world, workload, batch, seq, nasm, flops, arena_bytes, ms, max_
         "metric": "inferences_per_sec", "value": value, "unit": "inf/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": max_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32",
         "data": "synthetic",
-        "config": {"workload": f"{workload}_bs{batch}_per_gpu", "seq_len": seq or None, "tile_profile": "b200 128x128",
-                   "min_ninst_per_ldata": MIN_NINST, "tiles": nasm.num_ninst, "flops_per_step": flops,
+        "config": {"workload": f"{workload}_bs{batch}_per_gpu", "seq_len": seq or None, "tile_profile": "b200 tensor-core quanta",
+                   "tile_quanta": list(TILING[workload][:2]), "min_ninst_per_ldata": TILING[workload][2], "tiles": nasm.num_ninst, "flops_per_step": flops,
                    "l2": f"no flush: each step streams a {arena_bytes / 1e9:.2f} GB activation arena (> 126 MB L2)"},
         "clocks": clocks,
         "e2e": {"value": job_value(batch, args.steps, world, e2e_max), "unit": "inf/s", "h2d_bytes_per_step": int(x.nbytes),
