@@ -142,7 +142,7 @@ struct Engine {
     int num_sms = 0;
     unsigned n_ctas = 0;
     size_t smem_bytes = 0;
-    cudaStream_t stream = nullptr, side = nullptr;
+    cudaStream_t stream = nullptr, side = nullptr, io = nullptr;   // compute, stop flag, host transfers
     CtrlDev *ctrl = nullptr;
     StatusHost *status_h = nullptr;   // mapped host memory
     StatusHost *status_d = nullptr;
@@ -177,6 +177,14 @@ struct DeviceNasm {
     bool armed = false;  // has input, counters will be reset at the next run
     bool round_input = false;   // tensor-core path: the input is rounded to TF32 after upload
     bool ran = false;
+    // Transfers next to a running graph: only DMA goes to the transfer stream (a kernel could not start while the
+    // scheduler kernel holds every SM's shared memory); the scatter of a strided input and the gather of the last
+    // layer's result are kernels on the compute stream, ordered around the graph's own run.
+    float *in_stage = nullptr;          // packed input as uploaded, scattered into layer 0 just before the run
+    float *res_packed = nullptr;        // last layer gathered right after each run
+    cudaEvent_t in_consumed = nullptr;  // compute stream: in_stage has been scattered
+    cudaEvent_t res_ready = nullptr;    // compute stream: the run (and the gather) are complete
+    bool res_valid = false;
 };
 
 static bool env_u64(const char *name, unsigned long long *out) {
@@ -229,6 +237,7 @@ Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) 
     e->smem_bytes = (precision == 0 ? (size_t)tc::STAGES * tc::STAGE_BYTES + tc::EPI_BYTES : 0) + sizeof(tc::Shared) + 1024;
     bool ok = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&e->io, cudaStreamNonBlocking) == cudaSuccess &&
               cudaMalloc(&e->ctrl, sizeof(CtrlDev)) == cudaSuccess && cudaMemset(e->ctrl, 0, sizeof(CtrlDev)) == cudaSuccess &&
               cudaHostAlloc(&e->status_h, sizeof(StatusHost), cudaHostAllocMapped) == cudaSuccess &&
               cudaHostGetDevicePointer(&e->status_d, e->status_h, 0) == cudaSuccess;
@@ -258,6 +267,7 @@ void engine_destroy(Engine *e) {
     if (e->stream) cudaStreamSynchronize(e->stream);
     if (e->stream) cudaStreamDestroy(e->stream);
     if (e->side) cudaStreamDestroy(e->side);
+    if (e->io) cudaStreamDestroy(e->io);
     cudaFree(e->ctrl);
     if (e->status_h) cudaFreeHost((void *)e->status_h);
     cudaFree(e->queue);
@@ -277,6 +287,17 @@ static int to_device(T **dst, const std::vector<T> &src) {
     return 0;
 }
 
+// Stream for host <-> device transfers of one graph.  They run on a stream of their own so that the input
+// of the next graph uploads (and a finished graph's result downloads) while the scheduler kernel of
+// another graph is running; only a graph that is itself still being computed makes the transfer wait for
+// that run.
+static cudaStream_t io_stream(Engine *e, const nasm_t *nasm) {
+    if (e->running && std::find(e->in_flight.begin(), e->in_flight.end(), nasm) != e->in_flight.end() &&
+        *(volatile unsigned *)nasm->dev->completed_h == 0)
+        cudaStreamSynchronize(e->stream);
+    return e->io;
+}
+
 static int ensure_xfer(Engine *e, size_t bytes) {
     if (e->xfer_bytes >= bytes) return 0;
     cudaFree(e->xfer);
@@ -287,7 +308,10 @@ static int ensure_xfer(Engine *e, size_t bytes) {
     return 0;
 }
 
-// packed [W][H] <-> strided [W][ld] activation matrix
+// packed [W][H] <-> strided [W][ld] activation matrix.  Launched with 64-thread blocks: a block that small still
+// fits the registers the persistent scheduler kernel leaves free on an SM (it takes 11 warps x 168), so these
+// run next to a graph that is being computed instead of waiting for it.
+constexpr unsigned XFER_THREADS = 64;
 __global__ void unpack_columns(float *dst, const float *src, unsigned H, unsigned ld, size_t n, int round) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         size_t w = i / H;
@@ -352,6 +376,9 @@ static void free_device_nasm(DeviceNasm *dn) {
     cudaFree(dn->dep_init); cudaFree(dn->layer_done); cudaFree(dn->layer_tiles); cudaFree(dn->init_ready);
     cudaFree(dn->layers_completed); cudaFree(dn->wmaps);
     if (dn->completed_h) cudaFreeHost(dn->completed_h);
+    cudaFree(dn->in_stage); cudaFree(dn->res_packed);
+    if (dn->in_consumed) cudaEventDestroy(dn->in_consumed);
+    if (dn->res_ready) cudaEventDestroy(dn->res_ready);
     delete dn;
 }
 
@@ -546,6 +573,15 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
     *dn->completed_h = 0;
     CUDA_TRY(cudaHostGetDevicePointer(&dn->completed_d, dn->completed_h, 0));
 
+    {
+        const nasm_ldata_t &l0 = nasm->ldata[0], &ll = nasm->ldata[nasm->num_ldata - 1];
+        if (l0.out_mat_stride != l0.out_mat_dims[OUT_H])
+            CUDA_TRY(cudaMalloc(&dn->in_stage, std::max<size_t>((size_t)l0.out_mat_dims[OUT_H] * l0.out_mat_dims[OUT_W], 1) * sizeof(float)));
+        if (ll.out_mat_stride != ll.out_mat_dims[OUT_H])
+            CUDA_TRY(cudaMalloc(&dn->res_packed, std::max<size_t>((size_t)ll.out_mat_dims[OUT_H] * ll.out_mat_dims[OUT_W], 1) * sizeof(float)));
+        CUDA_TRY(cudaEventCreateWithFlags(&dn->in_consumed, cudaEventDisableTiming));
+        CUDA_TRY(cudaEventCreateWithFlags(&dn->res_ready, cudaEventDisableTiming));
+    }
     NasmDev &H = dn->host;
     memset(&H, 0, sizeof H);
     H.layers = dn->layers; H.tiles = dn->tiles; H.children = dn->children; H.dep = dn->dep; H.dep_init = dn->dep_init;
@@ -563,26 +599,33 @@ int engine_set_input(nasm_t *nasm, const void *input_host) {
     const nasm_ldata_t &l0 = nasm->ldata[0];
     const size_t n = (size_t)l0.out_mat_dims[OUT_H] * l0.out_mat_dims[OUT_W];
     float *dst = (float *)((char *)dn->arena + dn->ldata_off[0]);
+    cudaStream_t io = io_stream(e, nasm);
+    dn->res_valid = false;
     if (!input_host) {
+        // no input: layer 0 is cleared, on the compute stream, ahead of the graph's next run
         CUDA_TRY(cudaMemsetAsync(dst, 0, l0.out_mat_mem_size, e->stream));
         return 0;
     }
-    if (l0.out_mat_stride == l0.out_mat_dims[OUT_H]) {
-        CUDA_TRY(cudaMemcpyAsync(dst, input_host, n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
-    } else {
-        if (ensure_xfer(e, n * sizeof(float)) != 0) return -1;
-        CUDA_TRY(cudaMemcpyAsync(e->xfer, input_host, n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
-        unsigned blocks = (unsigned)std::min<size_t>((n + 255) / 256, 4096);
-        unpack_columns<<<blocks, 256, 0, e->stream>>>(dst, e->xfer, l0.out_mat_dims[OUT_H], l0.out_mat_stride, n, dn->round_input ? 1 : 0);
+    const unsigned blocks = (unsigned)std::min<size_t>((n + XFER_THREADS - 1) / XFER_THREADS, 16384);
+    if (dn->in_stage) {
+        // DMA into the staging copy (after the previous scatter has read it), then the scatter on the compute stream
+        CUDA_TRY(cudaStreamWaitEvent(io, dn->in_consumed, 0));
+        CUDA_TRY(cudaMemcpyAsync(dn->in_stage, input_host, n * sizeof(float), cudaMemcpyHostToDevice, io));
+        // The caller may reuse its buffer as soon as we return (the reference copies synchronously).
+        CUDA_TRY(cudaStreamSynchronize(io));
+        unpack_columns<<<blocks, XFER_THREADS, 0, e->stream>>>(dst, dn->in_stage, l0.out_mat_dims[OUT_H], l0.out_mat_stride, n, dn->round_input ? 1 : 0);
         e->launches++;
         CUDA_TRY(cudaGetLastError());
+        CUDA_TRY(cudaEventRecord(dn->in_consumed, e->stream));
+    } else {
+        CUDA_TRY(cudaMemcpyAsync(dst, input_host, n * sizeof(float), cudaMemcpyHostToDevice, io));
+        CUDA_TRY(cudaStreamSynchronize(io));
+        if (dn->round_input) {   // packed layout: round in place (the strided path rounds while scattering)
+            round_tf32_inplace<<<blocks, XFER_THREADS, 0, e->stream>>>(dst, n);
+            e->launches++;
+            CUDA_TRY(cudaGetLastError());
+        }
     }
-    if (dn->round_input && l0.out_mat_stride == l0.out_mat_dims[OUT_H]) {   // packed layout: round in place (the strided path rounds while scattering)
-        round_tf32_inplace<<<(unsigned)std::min<size_t>((n + 255) / 256, 4096), 256, 0, e->stream>>>(dst, n);
-        e->launches++;
-    }
-    // The caller may reuse its buffer as soon as we return (the reference copies synchronously).
-    CUDA_TRY(cudaStreamSynchronize(e->stream));
     return 0;
 }
 
@@ -592,6 +635,7 @@ int engine_attach_nasm(Engine *e, nasm_t *nasm, const void *input_host) {
     if (nasm->dev && nasm->dev->e != e) { engine_detach_nasm(nasm); }
     if (!nasm->dev) {
         if (build_device_nasm(e, nasm) != 0) { engine_detach_nasm(nasm); return -1; }
+        CUDA_TRY(cudaStreamSynchronize(e->stream));   // the image (zeroed arena, descriptors) is in place before the transfer stream touches it
     }
     if (engine_set_input(nasm, input_host) != 0) return -1;
     nasm->dev->armed = true;
@@ -669,6 +713,21 @@ static int launch_run(Engine *e, const std::vector<nasm_t *> &run) {
         sched::scheduler_kernel<false><<<e->n_ctas, sched::SCHED_THREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
     e->launches += 3;
     CUDA_TRY(cudaGetLastError());
+    for (nasm_t *nasm : run) {
+        DeviceNasm *dn = nasm->dev;
+        if (dn->res_packed) {
+            const unsigned last = nasm->num_ldata - 1;
+            const nasm_ldata_t &ld = nasm->ldata[last];
+            const size_t n = (size_t)ld.out_mat_dims[OUT_H] * ld.out_mat_dims[OUT_W];
+            const unsigned blocks = (unsigned)std::min<size_t>((n + XFER_THREADS - 1) / XFER_THREADS, 16384);
+            pack_columns<<<blocks, XFER_THREADS, 0, e->stream>>>(dn->res_packed, (const float *)((char *)dn->arena + dn->ldata_off[last]),
+                                                                ld.out_mat_dims[OUT_H], ld.out_mat_stride, n);
+            e->launches++;
+        }
+        CUDA_TRY(cudaEventRecord(dn->res_ready, e->stream));
+        dn->res_valid = true;
+    }
+    CUDA_TRY(cudaGetLastError());
     return 0;
 }
 
@@ -733,16 +792,24 @@ long engine_read_ldata(nasm_t *nasm, unsigned int idx, float *out) {
     const nasm_ldata_t &ld = nasm->ldata[idx];
     const size_t n = (size_t)ld.out_mat_dims[OUT_H] * ld.out_mat_dims[OUT_W];
     const float *src = (const float *)((char *)dn->arena + dn->ldata_off[idx]);
+    if (idx == nasm->num_ldata - 1 && dn->res_valid) {
+        // the last layer of a graph that has run: already gathered (or packed by layout); DMA only
+        if (cudaStreamWaitEvent(e->io, dn->res_ready, 0) != cudaSuccess) return -1;
+        if (cudaMemcpyAsync(out, dn->res_packed ? dn->res_packed : src, n * sizeof(float), cudaMemcpyDeviceToHost, e->io) != cudaSuccess) return -1;
+        if (cudaStreamSynchronize(e->io) != cudaSuccess) { ASPEN_ERR("CUDA error reading layer %u: %s\n", idx, cudaGetErrorString(cudaGetLastError())); return -1; }
+        return (long)n;
+    }
+    cudaStream_t st = io_stream(e, nasm);
     if (ld.out_mat_stride == ld.out_mat_dims[OUT_H]) {
-        if (cudaMemcpyAsync(out, src, n * sizeof(float), cudaMemcpyDeviceToHost, e->stream) != cudaSuccess) return -1;
+        if (cudaMemcpyAsync(out, src, n * sizeof(float), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
     } else {
         if (ensure_xfer(e, n * sizeof(float)) != 0) return -1;
-        unsigned blocks = (unsigned)std::min<size_t>((n + 255) / 256, 4096);
-        pack_columns<<<blocks, 256, 0, e->stream>>>(e->xfer, src, ld.out_mat_dims[OUT_H], ld.out_mat_stride, n);
+        unsigned blocks = (unsigned)std::min<size_t>((n + XFER_THREADS - 1) / XFER_THREADS, 16384);
+        pack_columns<<<blocks, XFER_THREADS, 0, st>>>(e->xfer, src, ld.out_mat_dims[OUT_H], ld.out_mat_stride, n);
         e->launches++;
-        if (cudaMemcpyAsync(out, e->xfer, n * sizeof(float), cudaMemcpyDeviceToHost, e->stream) != cudaSuccess) return -1;
+        if (cudaMemcpyAsync(out, e->xfer, n * sizeof(float), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
     }
-    if (cudaStreamSynchronize(e->stream) != cudaSuccess) { ASPEN_ERR("CUDA error reading layer %u: %s\n", idx, cudaGetErrorString(cudaGetLastError())); return -1; }
+    if (cudaStreamSynchronize(st) != cudaSuccess) { ASPEN_ERR("CUDA error reading layer %u: %s\n", idx, cudaGetErrorString(cudaGetLastError())); return -1; }
     return (long)n;
 }
 

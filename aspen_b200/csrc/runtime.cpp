@@ -214,8 +214,6 @@ static int native_order(const nasm_ldata_t &ld, LAYER_PARAMS *order, unsigned in
 static ssize_t ldata_output(void **out_ptr, nasm_t *nasm, unsigned int idx, const LAYER_PARAMS *order) {
     const nasm_ldata_t &ld = nasm->ldata[idx];
     const size_t n = (size_t)ld.out_mat_dims[OUT_H] * ld.out_mat_dims[OUT_W];
-    std::vector<float> packed(n);
-    if (engine_read_ldata(nasm, idx, packed.data()) < 0) return -1;
     LAYER_PARAMS org[MAX_TENSOR_DIMS];
     unsigned int dims[NUM_PARAM_ELEMENTS];
     int nd = native_order(ld, org, dims);
@@ -223,6 +221,16 @@ static ssize_t ldata_output(void **out_ptr, nasm_t *nasm, unsigned int idx, cons
     size_t prod = 1;
     for (int i = 0; i < nd; i++) prod *= dims[org[i]];
     float *out = (float *)calloc(n ? n : 1, sizeof(float));
+    bool same = order != nullptr && prod == n;
+    for (int i = 0; same && i < nd; i++) same = order[i] == org[i];
+    if (same || !order || prod != n) {
+        // the wanted order is the one the device keeps: straight into the caller's buffer
+        if (engine_read_ldata(nasm, idx, out) < 0) { free(out); return -1; }
+        *out_ptr = out;
+        return (ssize_t)(n * sizeof(float));
+    }
+    std::vector<float> packed(n);
+    if (engine_read_ldata(nasm, idx, packed.data()) < 0) { free(out); return -1; }
     if (prod != n || !order) {
         memcpy(out, packed.data(), n * sizeof(float));   // shape not expressible: hand back native order
     } else {

@@ -265,3 +265,43 @@ def test_residual_fused_into_producer_equals_separate_layer(name, batch, seq, mn
     assert "RESIDUAL" in types
     for i, (a, b) in enumerate(zip(*outs)):
         assert np.array_equal(a, b), f"layer {i + 1} ({types[i]}) differs"
+
+
+def test_two_graphs_in_flight_upload_and_download_overlap_a_run(workdir):
+    """The serving loop of bench.py's end-to-end leg: while one graph is being computed, the next graph's
+    input is uploaded and the previous graph's result is read.  Every result must equal the one the same
+    input gives when nothing overlaps."""
+    cfg, wf = harness.prepare("resnet50", workdir)
+    L = api.lib()
+    L.aspen_b200_set_tile_profile(1)
+    dnn = api.Dnn(cfg, wf)
+    pair = [api.Nasm(dnn, 4, 0, 100), api.Nasm(dnn, 4, 0, 100)]
+    L.aspen_b200_set_tile_profile(0)
+    rpool = api.Rpool()
+    group = api.DseGroup(0, 0)
+    group.set_rpool(rpool)
+    i0 = pair[0].ldata_info(0)
+    rng = np.random.default_rng(11)
+    xs = [rng.standard_normal((i0["W"], i0["H"]), dtype=np.float32) for _ in range(5)]
+    order = [api.BATCH, api.OUT_C, api.OUT_H, api.OUT_W]
+    want = []
+    for x in xs:                                   # nothing overlaps
+        rpool.add(pair[0], x); group.run(); group.wait(pair[0]); group.stop()
+        want.append(pair[0].result(order).copy())
+    got = []
+    cur = 0
+    rpool.add(pair[cur], xs[0]); group.run()
+    for step in range(len(xs)):
+        nxt = cur ^ 1
+        if step + 1 < len(xs):
+            rpool.add(pair[nxt], xs[step + 1])     # upload under the running graph
+        group.wait(pair[cur]); group.stop()
+        assert group.status() == 0
+        if step + 1 < len(xs):
+            group.run()
+        got.append(pair[cur].result(order).copy()) # download under the next graph's run
+        cur = nxt
+    for a, b in zip(want, got):
+        assert np.array_equal(a, b)
+    assert not np.array_equal(want[0], want[1])
+    group.close(); pair[1].close(); pair[0].close(); rpool.close(); dnn.close()
