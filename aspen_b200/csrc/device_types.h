@@ -26,6 +26,7 @@ struct LayerDev {
     unsigned a_kind, b_kind;  // operand staging, see tiles_tc.cuh
     unsigned a_vec4;          // activation rows can be fetched in 16-byte pieces (IC % 4 == 0 ...)
     unsigned round_out;       // store outputs rounded to TF32 (nearest): a tensor-core layer reads them
+    unsigned PH;              // A_TMA_ROWS: rows per sample of the zero-padded copy of the input image
     // A residual layer fused into this (convolution / matmul) layer's epilogue: besides its own output the tile
     // also writes res_out = act(own + res_in) for the same region.  res_out == nullptr: nothing fused.
     const float *res_in;

@@ -48,6 +48,7 @@ struct DeviceDnn {
     std::vector<float *> bias;
     std::vector<float *> anchors;
     std::vector<unsigned> kpad;
+    std::vector<float *> weight_rows;   // tensor-core path, input convolutions with <= 4 channels: k = (kh, [kw][4] padded to 32)
     std::vector<unsigned> ic_pad;     // conv on the network input with IC % 4 != 0: channels padded to this many (0: not padded)
     bool have[2] = {false, false};
 };
@@ -74,6 +75,7 @@ static int upload_weights(aspen_dnn_t *dnn, int device, int precision, DeviceDnn
         dd->anchors.assign(dnn->num_layers, nullptr);
         dd->kpad.assign(dnn->num_layers, 0);
         dd->ic_pad.assign(dnn->num_layers, 0);
+        dd->weight_rows.assign(dnn->num_layers, nullptr);
         dnn->dev[device] = dd;
     }
     *out = dd;
@@ -105,6 +107,19 @@ static int upload_weights(aspen_dnn_t *dnn, int device, int precision, DeviceDnn
                 }
             CUDA_TRY(cudaMalloc(&dd->weight[precision][i], padded.size() * sizeof(float) + 256));
             CUDA_TRY(cudaMemcpy(dd->weight[precision][i], padded.data(), padded.size() * sizeof(float), cudaMemcpyHostToDevice));
+            if (precision == 0 && l.type == CONV_LAYER && l.parent_layers[PARENT_0] && l.parent_layers[PARENT_0]->type == INPUT_LAYER && ic <= 4 &&
+                l.params[WEIGHT_W] <= 8 && !dd->weight_rows[i]) {
+                // second copy for the row-box staging: one 32-float chunk per filter row, (kw, channel) inside it
+                const unsigned KH = l.params[WEIGHT_H], KW = l.params[WEIGHT_W];
+                std::vector<float> rowsw((size_t)rows * KH * 32, 0.f);
+                for (unsigned r = 0; r < rows; r++)
+                    for (unsigned kh = 0; kh < KH; kh++)
+                        for (unsigned kw = 0; kw < KW; kw++)
+                            for (unsigned c = 0; c < ic; c++)
+                                rowsw[((size_t)r * KH + kh) * 32 + kw * 4 + c] = round_to_tf32(src[(size_t)r * k + (kh * KW + kw) * ic + c]);
+                CUDA_TRY(cudaMalloc(&dd->weight_rows[i], rowsw.size() * sizeof(float) + 256));
+                CUDA_TRY(cudaMemcpy(dd->weight_rows[i], rowsw.data(), rowsw.size() * sizeof(float), cudaMemcpyHostToDevice));
+            }
         }
         if (b && !dd->bias[i]) {
             CUDA_TRY(cudaMalloc(&dd->bias[i], (size_t)b->num_elements * sizeof(float) + 256));
@@ -128,6 +143,7 @@ void engine_release_dnn(aspen_dnn_t *dnn) {
         for (int p = 0; p < 2; p++)
             for (float *ptr : dd->weight[p]) cudaFree(ptr);
         for (float *ptr : dd->bias) cudaFree(ptr);
+        for (float *ptr : dd->weight_rows) cudaFree(ptr);
         for (float *ptr : dd->anchors) cudaFree(ptr);
         cudaSetDevice(prev);
         delete dd;
@@ -185,6 +201,9 @@ struct DeviceNasm {
     cudaEvent_t in_consumed = nullptr;  // compute stream: in_stage has been scattered
     cudaEvent_t res_ready = nullptr;    // compute stream: the run (and the gather) are complete
     bool res_valid = false;
+    // A_TMA_ROWS: zero-padded [sample][PH][PW][4] copy of the input image (borders stay zero), filled after each upload
+    float *padded_in = nullptr;
+    unsigned pin_ph = 0, pin_pw = 0, pin_pad = 0, pin_ic = 0, pin_ih = 0, pin_iw = 0;
 };
 
 static bool env_u64(const char *name, unsigned long long *out) {
@@ -312,6 +331,21 @@ static int ensure_xfer(Engine *e, size_t bytes) {
 // fits the registers the persistent scheduler kernel leaves free on an SM (it takes 11 warps x 168), so these
 // run next to a graph that is being computed instead of waiting for it.
 constexpr unsigned XFER_THREADS = 64;
+// layer-0 matrix [pixel][ld] (already rounded) -> interior of the zero-padded [sample][PH][PW][4] copy
+__global__ void fill_padded_input(float *dst, const float *src, unsigned ld, unsigned IC, unsigned IH, unsigned IW, unsigned PH, unsigned PW,
+                                  unsigned pad, size_t pixels) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < pixels; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t b = i / ((size_t)IH * IW), r = i - b * IH * IW;
+        const unsigned ih = (unsigned)(r / IW), iw = (unsigned)(r - (size_t)ih * IW);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float *p = src + i * ld;
+        v.x = p[0];
+        if (IC > 1) v.y = p[1];
+        if (IC > 2) v.z = p[2];
+        if (IC > 3) v.w = p[3];
+        reinterpret_cast<float4 *>(dst)[(b * PH + ih + pad) * PW + iw + pad] = v;
+    }
+}
 __global__ void unpack_columns(float *dst, const float *src, unsigned H, unsigned ld, size_t n, int round) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         size_t w = i / H;
@@ -376,7 +410,7 @@ static void free_device_nasm(DeviceNasm *dn) {
     cudaFree(dn->dep_init); cudaFree(dn->layer_done); cudaFree(dn->layer_tiles); cudaFree(dn->init_ready);
     cudaFree(dn->layers_completed); cudaFree(dn->wmaps);
     if (dn->completed_h) cudaFreeHost(dn->completed_h);
-    cudaFree(dn->in_stage); cudaFree(dn->res_packed);
+    cudaFree(dn->in_stage); cudaFree(dn->res_packed); cudaFree(dn->padded_in);
     if (dn->in_consumed) cudaEventDestroy(dn->in_consumed);
     if (dn->res_ready) cudaEventDestroy(dn->res_ready);
     delete dn;
@@ -413,6 +447,25 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
         maps.push_back(m);
         return (int)maps.size() - 1;
     };
+    // 3-D map of the padded input copy: (32 floats of a row, output pixel = `stride` input pixels apart, row)
+    // Eight consecutive maps, the j-th with a box of 16 j pixels.  Returns the index of the first, or -2 when the driver
+    // does not take such (overlapping) maps: the layer then keeps the gather.
+    auto add_rows_map = [&](const void *base, unsigned OW, unsigned stride, unsigned PW, cuuint64_t rows_total) -> int {
+        const size_t first = maps.size();
+        for (unsigned j = 1; j <= 8; j++) {
+            CUtensorMap m;
+            cuuint64_t dims[3] = {32, OW, rows_total};
+            cuuint64_t strides[2] = {(cuuint64_t)stride * 16, (cuuint64_t)PW * 16};
+            cuuint32_t box[3] = {32, std::min(16 * j, OW), 1}, estr[3] = {1, 1, 1};
+            CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(base), dims, strides, box, estr,
+                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) { maps.resize(first); return -2; }
+            maps.push_back(m);
+        }
+        return (int)first;
+    };
+    const char *no_rows = getenv("ASPEN_B200_NO_ROW_BOXES");
     for (unsigned i = 0; i < nasm->num_ldata; i++) {
         const aspen_layer_t &l = *nasm->ldata[i].layer;
         LayerDev &L = layers[i];
@@ -424,13 +477,40 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
         const bool gemm_w = l.type == CONV_LAYER || l.type == FC_LAYER || l.type == MATMUL_LAYER;
         const unsigned p0 = nasm->ldata[i].parent_ldata_idx_arr[PARENT_0], p1 = nasm->ldata[i].parent_ldata_idx_arr[PARENT_1];
         const cuuint64_t W0 = p0 != (unsigned)-1 ? nasm->ldata[p0].out_mat_dims[OUT_W] : 0;
+        // Row-box staging of an input convolution (see tiles_tc.cuh, A_TMA_ROWS): decided first, it changes the
+        // weight layout the weight map is made from.
+        bool rows_kind = false;
+        if (l.type == CONV_LAYER && p0 == 0 && dn->dd->weight_rows[i] && !dn->padded_in && !(no_rows && atoi(no_rows) != 0) &&
+            L.OW % 16 == 0 && nasm->ldata[i].out_mat_dims[OUT_W] % 128 == 0 && nasm->ldata[i].ninst_tile_dims[OUT_W] % 128 == 0) {
+            const unsigned s_ = L.stride, pad = L.pad;
+            const unsigned PW = std::max(L.IW + 2 * pad, s_ * (L.OW - 1) + 8), PH = std::max(L.IH + 2 * pad, s_ * (L.OH - 1) + L.KH);
+            const size_t bytes = (size_t)nasm->batch_size * PH * PW * 4 * sizeof(float);
+            CUDA_TRY(cudaMalloc(&dn->padded_in, bytes + 256));
+            CUDA_TRY(cudaMemsetAsync(dn->padded_in, 0, bytes + 256, e->stream));
+            const int m = add_rows_map(dn->padded_in, L.OW, s_, PW, (cuuint64_t)nasm->batch_size * PH);
+            if (m >= 0) {
+                dn->pin_ph = PH; dn->pin_pw = PW; dn->pin_pad = pad; dn->pin_ic = l.params[IN_C]; dn->pin_ih = L.IH; dn->pin_iw = L.IW;
+                rows_kind = true;
+                L.a_kind = tc::A_TMA_ROWS;
+                L.amap = m;
+                L.PH = PH;
+                L.weight = dn->dd->weight_rows[i];
+                L.Kpad = L.KH * 32;
+                L.K = L.Kpad;
+            } else {
+                cudaFree(dn->padded_in);
+                dn->padded_in = nullptr;
+            }
+        }
         if (gemm_w) {
             L.b_kind = tc::B_TMA;
-            L.wmap = add_map(dn->dd->weight[0][i], dn->dd->kpad[i], layer_weight_rows(&l), (cuuint64_t)dn->dd->kpad[i] * sizeof(float), 64);
+            L.wmap = add_map(L.weight, L.Kpad, layer_weight_rows(&l), (cuuint64_t)L.Kpad * sizeof(float), 64);
             if (L.wmap < 0) return -1;
         }
         const bool aligned0 = L.ld0 % 4 == 0;
-        if (l.type == MATMUL_LAYER && aligned0 && L.K % 4 == 0) {
+        if (rows_kind) {
+            // operands set above
+        } else if (l.type == MATMUL_LAYER && aligned0 && L.K % 4 == 0) {
             L.a_kind = tc::A_TMA;
             L.amap = add_map(L.in0, L.H0, W0, (cuuint64_t)L.ld0 * sizeof(float), 128);
         } else if (l.type == CONV_LAYER && aligned0 && L.IC % 4 == 0 && L.KH == 1 && L.KW == 1 && L.stride == 1 && L.pad == 0) {
@@ -604,6 +684,7 @@ int engine_set_input(nasm_t *nasm, const void *input_host) {
     if (!input_host) {
         // no input: layer 0 is cleared, on the compute stream, ahead of the graph's next run
         CUDA_TRY(cudaMemsetAsync(dst, 0, l0.out_mat_mem_size, e->stream));
+        if (dn->padded_in) CUDA_TRY(cudaMemsetAsync(dn->padded_in, 0, (size_t)nasm->batch_size * dn->pin_ph * dn->pin_pw * 4 * sizeof(float), e->stream));
         return 0;
     }
     const unsigned blocks = (unsigned)std::min<size_t>((n + XFER_THREADS - 1) / XFER_THREADS, 16384);
@@ -625,6 +706,13 @@ int engine_set_input(nasm_t *nasm, const void *input_host) {
             e->launches++;
             CUDA_TRY(cudaGetLastError());
         }
+    }
+    if (dn->padded_in) {
+        const size_t pixels = l0.out_mat_dims[OUT_W];
+        fill_padded_input<<<(unsigned)std::min<size_t>((pixels + 255) / 256, 8192), 256, 0, e->stream>>>(
+            dn->padded_in, dst, l0.out_mat_stride, dn->pin_ic, dn->pin_ih, dn->pin_iw, dn->pin_ph, dn->pin_pw, dn->pin_pad, pixels);
+        e->launches++;
+        CUDA_TRY(cudaGetLastError());
     }
     return 0;
 }

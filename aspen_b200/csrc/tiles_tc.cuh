@@ -123,6 +123,11 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const void *tmap, int 
                  ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(unsigned dst, const void *tmap, int x, int y, int z, unsigned long long *bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(unsigned *holder, unsigned cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -256,11 +261,16 @@ __device__ __forceinline__ void store_block_residual(float *stage, const float *
 //           A_TMA_FIXUP  stride-1 "same" convolution: tap (kh, kw) of 128 consecutive output pixels is the parent
 //                        matrix shifted by (kh-p)*IW + (kw-p) columns, except where the tap leaves the image; the
 //                        box is loaded shifted and the owner thread of each such row overwrites it with zeros
+//           A_TMA_ROWS   convolution on the network input with <= 4 channels (the 7x7 stem): the input is kept as a
+//                        zero-padded [sample][row][pixel][4] copy, the k axis is (kh, [kw][4] padded to 32), so
+//                        one k-chunk of an output pixel is ONE contiguous 128-byte run of an input row, and 16 j
+//                        consecutive output pixels of a row are a 3-D box (32 floats, 16 j pixels `stride` apart, 1
+//                        row): two such boxes per chunk (cut at the end of an output row), no gather, no borders
 //   W side  B_TMA        64-row boxes of the [rows][Kpad] weight copy
 //           B_TMA_ACT    64-row boxes of the PARENT_1 activation matrix (attention keys)
 //           B_GATHER     cp.async rows of PARENT_1 (attention keys whose head size is not a multiple of 32)
 //           B_TRANSPOSED 4-byte cp.async transposing gather (attention values: W(m,k) = V[token k][feature m])
-enum { A_GATHER = 0, A_TMA = 1, A_TMA_FIXUP = 2 };
+enum { A_GATHER = 0, A_TMA = 1, A_TMA_FIXUP = 2, A_TMA_ROWS = 3 };
 enum { B_GATHER = 0, B_TMA = 1, B_TMA_ACT = 2, B_TRANSPOSED = 3 };
 
 struct Operands {
@@ -323,7 +333,7 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
     const unsigned tmem = sh->tmem_base;
     const unsigned a_kind = L.a_kind, b_kind = L.b_kind;
     const bool a_tma = a_kind != A_GATHER, b_tma = b_kind == B_TMA || b_kind == B_TMA_ACT;
-    const bool worker_work = a_kind != A_TMA || !b_tma;      // workers write shared memory in this layer
+    const bool worker_work = (a_kind != A_TMA && a_kind != A_TMA_ROWS) || !b_tma;      // workers write shared memory in this layer
     const void *amap = a_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.amap * 128) : nullptr;
     const void *bmap = b_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.wmap * 128) : nullptr;
     const bool vec_x = L.a_vec4 != 0;
@@ -435,7 +445,20 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                             const unsigned bytes = (a_tma ? A_STAGE_BYTES : 0u) + (b_tma ? NB * 128u : 0u);
                             if (bytes) mbar_arrive_expect_tx(&sh->landed[s], bytes);
                             else mbar_arrive(&sh->landed[s]);
-                            if (a_tma) {
+                            if (a_kind == A_TMA_ROWS) {
+                                // chunk kc / 32 is filter row kh.  The 128 pixels are cut where an output row ends; a run of
+                                // 16 j pixels uses the j-th of the layer's consecutive tensor maps (box of 16 j pixels).
+                                const unsigned hw = L.OH * L.OW;
+                                #pragma unroll 1
+                                for (unsigned done = 0; done < 128u;) {
+                                    const unsigned n = T.pos_w + n0 + done;
+                                    const unsigned b = n / hw, r = n - b * hw, oh = r / L.OW, ow = r - oh * L.OW;
+                                    const unsigned len = min(128u - done, L.OW - ow);
+                                    tma_load_3d(sA + done * 128u, (const unsigned char *)amap + (size_t)(len / 16u - 1u) * 128, 0, (int)ow,
+                                                (int)(b * L.PH + oh * L.stride + (kc >> 5)), &sh->landed[s]);
+                                    done += len;
+                                }
+                            } else if (a_tma) {
                                 int x = op.ax + (int)kc, y = op.ay + (int)n0;
                                 if (a_kind == A_TMA_FIXUP) {
                                     const unsigned tap = kc / L.IC;
