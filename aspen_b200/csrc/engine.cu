@@ -465,6 +465,28 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
         }
         return (int)first;
     };
+    // Maps of the im2col staging (A_TMA_IM2COL): the parent as (channel, iw, ih, sample), element stride = convolution
+    // stride on iw and ih.  Index L - 1: a run of L pixels of one output row; index OW + k - 2: k whole output rows.
+    auto add_im2col_maps = [&](const void *base, unsigned C, unsigned IW, unsigned IH, unsigned B, unsigned ld, unsigned stride, unsigned OW,
+                               unsigned OH) -> int {
+        const size_t first = maps.size();
+        const unsigned kmax = std::max(1u, std::min(OH, 128u / OW));
+        for (unsigned idx = 0; idx < OW + kmax - 1; idx++) {
+            const unsigned len = idx < OW ? idx + 1 : OW, rows = idx < OW ? 1 : idx - OW + 2;
+            CUtensorMap m;
+            cuuint64_t dims[4] = {C, IW, IH, B};
+            cuuint64_t strides[3] = {(cuuint64_t)ld * 4, (cuuint64_t)IW * ld * 4, (cuuint64_t)IH * IW * ld * 4};
+            cuuint32_t box[4] = {32, len * stride, rows * stride, 1}, estr[4] = {1, stride, stride, 1};
+            CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void *>(base), dims, strides, box, estr,
+                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) { maps.resize(first); return -2; }
+            maps.push_back(m);
+        }
+        return (int)first;
+    };
+    unsigned long long im2col_mode = 1;   // 0: off, 1: convolutions that would otherwise gather, 2: also the stride-1 "same" ones
+    env_u64("ASPEN_B200_IM2COL", &im2col_mode);
     const char *no_rows = getenv("ASPEN_B200_NO_ROW_BOXES");
     for (unsigned i = 0; i < nasm->num_ldata; i++) {
         const aspen_layer_t &l = *nasm->ldata[i].layer;
@@ -517,9 +539,13 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
             L.a_kind = tc::A_TMA;
             L.amap = add_map(L.in0, L.H0, W0, (cuuint64_t)L.ld0 * sizeof(float), 128);
         } else if (l.type == CONV_LAYER && aligned0 && L.IC % 32 == 0 && L.stride == 1 && L.OH == L.IH && L.OW == L.IW && L.KH == L.KW &&
-                   2 * L.pad + 1 == L.KH) {
+                   2 * L.pad + 1 == L.KH && im2col_mode != 2) {
             L.a_kind = tc::A_TMA_FIXUP;
             L.amap = add_map(L.in0, L.H0, W0, (cuuint64_t)L.ld0 * sizeof(float), 128);
+        } else if (l.type == CONV_LAYER && aligned0 && L.IC % 32 == 0 && L.IC == L.H0 && im2col_mode != 0 && L.OW * L.stride <= 256 &&
+                   L.stride <= 8 && L.OW <= 128 && L.KH * L.KW * L.IC == L.K) {
+            const int m = add_im2col_maps(L.in0, L.IC, L.IW, L.IH, nasm->batch_size, L.ld0, L.stride, L.OW, L.OH);
+            if (m >= 0) { L.a_kind = tc::A_TMA_IM2COL; L.amap = m; }
         } else if (l.type == FC_LAYER && L.ld0 == L.IC && L.K % 4 == 0) {
             L.a_kind = tc::A_TMA;   // a sample's NHWC activations are one contiguous row of K values
             L.amap = add_map(L.in0, L.K, nasm->batch_size, (cuuint64_t)L.IH * L.IW * L.ld0 * sizeof(float), 128);

@@ -128,6 +128,11 @@ __device__ __forceinline__ void tma_load_3d(unsigned dst, const void *tmap, int 
                  ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(unsigned dst, const void *tmap, int x, int y, int z, int w, unsigned long long *bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(unsigned *holder, unsigned cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -266,11 +271,17 @@ __device__ __forceinline__ void store_block_residual(float *stage, const float *
 //                        one k-chunk of an output pixel is ONE contiguous 128-byte run of an input row, and 16 j
 //                        consecutive output pixels of a row are a 3-D box (32 floats, 16 j pixels `stride` apart, 1
 //                        row): two such boxes per chunk (cut at the end of an output row), no gather, no borders
+//           A_TMA_IM2COL any convolution with IC % 32 == 0: the parent matrix seen as a 4-D tensor (channel, iw, ih,
+//                        sample) with the convolution stride as TMA element stride.  One k-chunk = 32 channels of one
+//                        tap; the 128 output pixels are cut into runs (rest of an output row, whole rows up to the end
+//                        of the sample, ...) and each run is one box whose first pixel is (ow*s + kw - p, oh*s + kh - p):
+//                        padding taps fall outside the tensor and arrive as zeros.  No gather, no fix-up; a handful
+//                        of boxes per chunk, each run length with its own tensor map
 //   W side  B_TMA        64-row boxes of the [rows][Kpad] weight copy
 //           B_TMA_ACT    64-row boxes of the PARENT_1 activation matrix (attention keys)
 //           B_GATHER     cp.async rows of PARENT_1 (attention keys whose head size is not a multiple of 32)
 //           B_TRANSPOSED 4-byte cp.async transposing gather (attention values: W(m,k) = V[token k][feature m])
-enum { A_GATHER = 0, A_TMA = 1, A_TMA_FIXUP = 2, A_TMA_ROWS = 3 };
+enum { A_GATHER = 0, A_TMA = 1, A_TMA_FIXUP = 2, A_TMA_ROWS = 3, A_TMA_IM2COL = 4 };
 enum { B_GATHER = 0, B_TMA = 1, B_TMA_ACT = 2, B_TRANSPOSED = 3 };
 
 struct Operands {
@@ -333,7 +344,7 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
     const unsigned tmem = sh->tmem_base;
     const unsigned a_kind = L.a_kind, b_kind = L.b_kind;
     const bool a_tma = a_kind != A_GATHER, b_tma = b_kind == B_TMA || b_kind == B_TMA_ACT;
-    const bool worker_work = (a_kind != A_TMA && a_kind != A_TMA_ROWS) || !b_tma;      // workers write shared memory in this layer
+    const bool worker_work = (a_kind != A_TMA && a_kind != A_TMA_ROWS && a_kind != A_TMA_IM2COL) || !b_tma;      // workers write shared memory in this layer
     const void *amap = a_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.amap * 128) : nullptr;
     const void *bmap = b_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.wmap * 128) : nullptr;
     const bool vec_x = L.a_vec4 != 0;
@@ -442,7 +453,7 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                     } else if (tid == TMA_THREAD) {
                         if (!ps.dead && !mbar_wait(&sh->empty[s], ph ^ 1u, ctrl, status, 2)) ps.dead = true;
                         if (!ps.dead) {
-                            const unsigned bytes = (a_tma ? A_STAGE_BYTES : 0u) + (b_tma ? NB * 128u : 0u);
+                            const unsigned bytes = (a_tma ? (a_kind == A_TMA_IM2COL ? rows_valid * 128u : A_STAGE_BYTES) : 0u) + (b_tma ? NB * 128u : 0u);
                             if (bytes) mbar_arrive_expect_tx(&sh->landed[s], bytes);
                             else mbar_arrive(&sh->landed[s]);
                             if (a_kind == A_TMA_ROWS) {
@@ -456,6 +467,20 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                                     const unsigned len = min(128u - done, L.OW - ow);
                                     tma_load_3d(sA + done * 128u, (const unsigned char *)amap + (size_t)(len / 16u - 1u) * 128, 0, (int)ow,
                                                 (int)(b * L.PH + oh * L.stride + (kc >> 5)), &sh->landed[s]);
+                                    done += len;
+                                }
+                            } else if (a_kind == A_TMA_IM2COL) {
+                                const unsigned tap = kc / L.IC, c0 = kc - tap * L.IC, kh = tap / L.KW, kw = tap - kh * L.KW;
+                                const unsigned hw = L.OH * L.OW;
+                                #pragma unroll 1
+                                for (unsigned done = 0; done < rows_valid;) {
+                                    const unsigned n = T.pos_w + n0 + done, rem = rows_valid - done;
+                                    const unsigned b = n / hw, r = n - b * hw, oh = r / L.OW, ow = r - oh * L.OW;
+                                    unsigned len, mi;
+                                    if (ow != 0u || rem < L.OW) { len = min(rem, L.OW - ow); mi = len - 1u; }          // (rest of) one output row
+                                    else { const unsigned k = min(rem / L.OW, L.OH - oh); len = k * L.OW; mi = L.OW + k - 2u; }   // k whole rows
+                                    tma_load_4d(sA + done * 128u, (const unsigned char *)amap + (size_t)mi * 128, (int)c0,
+                                                (int)(ow * L.stride + kw) - (int)L.pad, (int)(oh * L.stride + kh) - (int)L.pad, (int)b, &sh->landed[s]);
                                     done += len;
                                 }
                             } else if (a_tma) {
