@@ -35,7 +35,7 @@ WORKLOADS = {
     "bert_base": ("bert_base", 32, 128, "n002", 3, 3),
 }
 # DRAM bytes per scheduler launch, from the ncu capture summarised in profiles/ (batch-4 case scaled by 8).
-TRAFFIC_BYTES = {"resnet50": 2.5e9}
+TRAFFIC_BYTES = {"resnet50": 2.3e9}
 # Tiling of the nasm per workload: (row quantum, column quantum, min_ninst_per_ldata).  Tensor-core shaped
 # quanta; the values a graph computes do not depend on them.  Each is the best of a measured sweep
 # (quanta 64-256, min_ninst 100-592).

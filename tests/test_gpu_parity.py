@@ -108,12 +108,20 @@ def test_rerun_is_bitwise_identical_and_batch_samples_are_independent(workdir):
     assert dev.rerun() == 0                    # rpool_reset_nasm keeps the input resident in layer 0
     assert np.array_equal(first, dev.nasm.ldata(last)) and np.array_equal(mid, dev.nasm.ldata(40))
     dev.close()
-    # sample 2 alone gives the same logits as sample 2 inside the batch (tiles never mix samples)
-    one = harness.Device(cfg, wf, 1, 0, 50, 0, 0)
+    # sample 2 alone gives the same logits as sample 2 inside the batch (tiles never mix samples) ...
+    one = harness.Device(cfg, wf, 1, 0, 50, 0, 1)
     per = x.shape[0] // 4
     assert one.run(x[2 * per:3 * per]) == 0
     np.testing.assert_array_equal(one.nasm.ldata(last)[0], first[2])
     one.close()
+    # ... and with the reference's tile geometry too, up to the TF32 summation order of the input
+    # convolution (its k axis is staged in a different order when the tiles are whole MMA blocks)
+    ref_geom = harness.Device(cfg, wf, 1, 0, 50, 0, 0)
+    assert ref_geom.run(x[2 * per:3 * per]) == 0
+    got = ref_geom.nasm.ldata(last)[0]
+    assert np.abs(got - first[2]).max() <= 2e-3 * np.abs(first[2]).max()
+    assert int(got.argmax()) == int(first[2].argmax())
+    ref_geom.close()
 
 
 def test_result_api_orders(workdir):
