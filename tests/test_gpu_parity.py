@@ -84,14 +84,33 @@ def test_every_layer_matches_oracle(name, batch, seq, mn, precision, profile, wo
 
 
 @pytest.mark.skipif(not ref.available(), reason="needs the reference build")
+@pytest.mark.parametrize("env", [{"ASPEN_B200_NO_ROW_BOXES": "1"}, {"ASPEN_B200_IM2COL": "0"}, {"ASPEN_B200_IM2COL": "2"},
+                                 {"ASPEN_B200_NO_FUSE": "1", "ASPEN_B200_IM2COL": "2"}])
+def test_every_operand_staging_matches_oracle(env, workdir, monkeypatch):
+    """ResNet-50 with each way of staging the convolution operands forced: stem by gather instead of row boxes,
+    strided layers by gather instead of strided boxes, every 3x3 layer by strided boxes instead of shifted
+    box + fix-up.  All must meet the same per-layer bound against the reference."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    cfg, wf = harness.prepare("resnet50", workdir)
+    dev = harness.Device(cfg, wf, 3, 0, 100, 0, 1)
+    x = harness.make_input("resnet50", dev.input_shape())
+    assert dev.run(x) == 0, api.last_error()
+    outs = oracle_layers("resnet50", cfg, wf, 3, 0, 100, x)
+    worst = check_layers(dev, outs, 0, "resnet50")
+    assert worst < TF32_NORM
+    dev.close()
+
+
+@pytest.mark.skipif(not ref.available(), reason="needs the reference build")
 @pytest.mark.parametrize("name,batch,seq", [("resnet50", 32, 0), ("bert_base", 32, 128)])
 def test_benchmark_configuration_matches_oracle(name, batch, seq, workdir):
     """The benchmark's own workload (batch 32, B200 tile profile, TF32) against the reference."""
     cfg, wf = harness.prepare(name, workdir)
-    dev = harness.Device(cfg, wf, batch, seq, 296, 0, 1)
+    dev = harness.Device(cfg, wf, batch, seq, 148, 0, 1)
     x = harness.make_input(name, dev.input_shape())
     assert dev.run(x) == 0, api.last_error()
-    outs = oracle_layers(name, cfg, wf, batch, seq, 296, x)
+    outs = oracle_layers(name, cfg, wf, batch, seq, 148, x)
     worst = check_layers(dev, outs, 0, name)
     assert worst < TF32_NORM
     dev.close()
