@@ -27,6 +27,8 @@ struct LayerDev {
     unsigned a_vec4;          // activation rows can be fetched in 16-byte pieces (IC % 4 == 0 ...)
     unsigned round_out;       // store outputs rounded to TF32 (nearest): a tensor-core layer reads them
     unsigned PH;              // A_TMA_ROWS: rows per sample of the zero-padded copy of the input image
+    unsigned bw;              // tile columns per accumulator block: 128, or whole output rows / samples (A_TMA_IM2COL, one box)
+    unsigned one_box;         // A_TMA_IM2COL: index of the single tensor map that covers a block (bw != 128)
     // A residual layer fused into this (convolution / matmul) layer's epilogue: besides its own output the tile
     // also writes res_out = act(own + res_in) for the same region.  res_out == nullptr: nothing fused.
     const float *res_in;

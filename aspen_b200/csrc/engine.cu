@@ -395,6 +395,7 @@ static void fill_layer(const nasm_t *nasm, const DeviceNasm *dn, unsigned i, int
     L.seq = nasm->tr_seq_len; L.heads = p[NUM_HEAD]; L.hd = p[NUM_HEAD] ? p[NUM_HIDDEN] / p[NUM_HEAD] : 0; L.masked = p[MASKED];
     L.p_out_c = p[OUT_C]; L.p_in_c = p[IN_C]; L.p_stride = p[STRIDE];
     L.wmap = wmap_idx;
+    L.bw = 128;
     switch (l.type) {
         case CONV_LAYER: case FC_LAYER: L.a_vec4 = (L.IC % 4 == 0) && (L.ld0 % 4 == 0); break;
         case MATMUL_LAYER: L.a_vec4 = (L.K % 4 == 0) && (L.ld0 % 4 == 0); break;
@@ -483,6 +484,17 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
             if (r != CUDA_SUCCESS) { maps.resize(first); return -2; }
             maps.push_back(m);
         }
+        if (OW * OH <= 128) {   // last map: whole samples (a block of conv_block_width pixels)
+            CUtensorMap m;
+            cuuint64_t dims[4] = {C, IW, IH, B};
+            cuuint64_t strides[3] = {(cuuint64_t)ld * 4, (cuuint64_t)IW * ld * 4, (cuuint64_t)IH * IW * ld * 4};
+            cuuint32_t box[4] = {32, OW * stride, OH * stride, 128 / (OW * OH)}, estr[4] = {1, stride, stride, 1};
+            CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void *>(base), dims, strides, box, estr,
+                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) { maps.resize(first); return -2; }
+            maps.push_back(m);
+        }
         return (int)first;
     };
     unsigned long long im2col_mode = 1;   // 0: off, 1: convolutions that would otherwise gather, 2: also the stride-1 "same" ones
@@ -545,7 +557,17 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
         } else if (l.type == CONV_LAYER && aligned0 && L.IC % 32 == 0 && L.IC == L.H0 && im2col_mode != 0 && L.OW * L.stride <= 256 &&
                    L.stride <= 8 && L.OW <= 128 && L.KH * L.KW * L.IC == L.K) {
             const int m = add_im2col_maps(L.in0, L.IC, L.IW, L.IH, nasm->batch_size, L.ld0, L.stride, L.OW, L.OH);
-            if (m >= 0) { L.a_kind = tc::A_TMA_IM2COL; L.amap = m; }
+            if (m >= 0) {
+                L.a_kind = tc::A_TMA_IM2COL;
+                L.amap = m;
+                // Tiles made of blocks of whole output rows / samples (the tiler does that for these layers when the column
+                // quantum is 128): each block is then one box.
+                const unsigned bw = conv_block_width(L.OW, L.OH), kmax = std::max(1u, std::min(L.OH, 128u / L.OW));
+                if (bw != 128 && conv_uses_row_blocks(&l) && nasm->ldata[i].ninst_tile_dims[OUT_W] % bw == 0) {
+                    L.bw = bw;
+                    L.one_box = L.OW * L.OH <= 128 ? L.OW + kmax - 1 : L.OW + bw / L.OW - 2;
+                }
+            }
         } else if (l.type == FC_LAYER && L.ld0 == L.IC && L.K % 4 == 0) {
             L.a_kind = tc::A_TMA;   // a sample's NHWC activations are one contiguous row of K values
             L.amap = add_map(L.in0, L.K, nasm->batch_size, (cuuint64_t)L.IH * L.IW * L.ld0 * sizeof(float), 128);

@@ -134,6 +134,28 @@ unsigned int layer_contraction_k(const aspen_layer_t *l);
 unsigned int layer_weight_rows(const aspen_layer_t *l);
 // tiler.cpp
 extern TileQuanta g_quanta;
+
+// Output pixels per block of a convolution staged by strided TMA boxes, chosen so that a block is whole output
+// rows of one sample (or whole samples when a sample has at most 128 pixels): the block is then a single box.
+inline unsigned conv_block_width(unsigned OW, unsigned OH) {
+    if (OW == 0 || OH == 0 || OW > 128) return 128;
+    if (OW * OH <= 128) return (128 / (OW * OH)) * OW * OH;
+    unsigned k = 1;
+    for (unsigned d = 1; d <= OH && d * OW <= 128; d++)
+        if (OH % d == 0) k = d;
+    return k * OW;
+}
+// The convolutions that get that staging when tiles are whole MMA blocks (column quantum 128): IC a multiple of
+// 32 and neither a 1x1 stride-1 layer (plain 2-D boxes) nor a stride-1 "same" layer (shifted box + fix-up).
+inline bool conv_uses_row_blocks(const aspen_layer_t *l) {
+    if (l->type != CONV_LAYER) return false;
+    const unsigned *p = l->params;
+    const unsigned s = p[STRIDE] ? p[STRIDE] : 1;
+    if (p[IN_C] % 32 != 0 || p[OUT_W] > 128 || p[OUT_W] * s > 256 || s > 8) return false;
+    if (p[WEIGHT_H] == 1 && p[WEIGHT_W] == 1 && s == 1 && p[PADDING] == 0) return false;
+    if (s == 1 && p[OUT_H] == p[IN_H] && p[OUT_W] == p[IN_W] && p[WEIGHT_H] == p[WEIGHT_W] && 2 * p[PADDING] + 1 == p[WEIGHT_H]) return false;
+    return true;
+}
 void tiler_init_ldata(nasm_t *nasm, nasm_ldata_t *ld, aspen_layer_t *layer);
 void tiler_init_ninst(nasm_ldata_t *ld, ninst_t *ni, unsigned int ninst_idx);
 void out_mat_pos_from_tensor_pos(const nasm_ldata_t *ld, const unsigned int *tpos, unsigned int *mpos);

@@ -71,12 +71,21 @@ static bool out_mat_info(nasm_ldata_t *ld) {
 }
 
 // First guess: grow a (h_min x w_min) tile until it holds flop_per_ninst of work, rows first.
+// Column quantum of a layer: the global one, except for convolutions staged by strided TMA boxes when tiles are
+// whole MMA blocks -- their tiles are made of blocks of whole output rows (conv_block_width).
+static unsigned int layer_w_quantum(const nasm_ldata_t *ld) {
+    const TileQuanta &q = ld->nasm->quanta;
+    if (q.w_min == 128 && conv_uses_row_blocks(ld->layer)) return conv_block_width(ld->layer->params[OUT_W], ld->layer->params[OUT_H]);
+    return q.w_min;
+}
+
 static void initial_tile_dims(nasm_ldata_t *ld) {
     const TileQuanta &q = ld->nasm->quanta;
+    const unsigned int w_min = layer_w_quantum(ld);
     unsigned int *t = ld->ninst_tile_dims;
     const unsigned int *dim = ld->out_mat_dims;
     t[OUT_H] = q.h_min < dim[OUT_H] ? q.h_min : dim[OUT_H];
-    t[OUT_W] = q.w_min < dim[OUT_W] ? q.w_min : dim[OUT_W];
+    t[OUT_W] = w_min < dim[OUT_W] ? w_min : dim[OUT_W];
     if (t[OUT_H] == 0) t[OUT_H] = 1;
     if (t[OUT_W] == 0) t[OUT_W] = 1;
     const unsigned int want = ld->flop_per_output ? ld->nasm->flop_per_ninst / ld->flop_per_output : 0;
@@ -87,7 +96,7 @@ static void initial_tile_dims(nasm_ldata_t *ld) {
     }
     t[OUT_H] = (unsigned int)round_up(t[OUT_H], q.h_min);
     if (ld->layer->type != FC_LAYER && ld->layer->type != SOFTMAX_LAYER)
-        t[OUT_W] = (unsigned int)round_up(t[OUT_W], q.w_min);
+        t[OUT_W] = (unsigned int)round_up(t[OUT_W], w_min);
 }
 
 void tiler_init_ldata(nasm_t *nasm, nasm_ldata_t *ld, aspen_layer_t *layer) {
@@ -108,7 +117,7 @@ void tiler_init_ldata(nasm_t *nasm, nasm_ldata_t *ld, aspen_layer_t *layer) {
     unsigned int *t = ld->ninst_tile_dims;
     const unsigned int *dim = ld->out_mat_dims;
     const LAYER_TYPE type = layer->type;
-    unsigned int unit_h = q.h_min, unit_w = q.w_min, hidden_per_head = 0;
+    unsigned int unit_h = q.h_min, unit_w = layer_w_quantum(ld), hidden_per_head = 0;
     const bool whole_column = type == SOFTMAX_LAYER || type == APPEND_LAYER || type == YOLO_LAYER;
     if (whole_column) t[OUT_H] = (unsigned int)round_up(dim[OUT_H], q.h_min);
     if (type == SOFTMAX_LAYER) t[OUT_W] = 1;

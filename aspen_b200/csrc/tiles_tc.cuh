@@ -353,8 +353,9 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
     // ago; TMA reads them through the async proxy.
     if (tid == TMA_THREAD && a_tma) asm volatile("fence.proxy.async.global;" ::: "memory");
 
-    for (unsigned n0 = 0; n0 < T.tile_w; n0 += 128) {
-        const unsigned rows_valid = min(128u, T.tile_w - n0);
+    const unsigned bw = L.bw;   // 128 except for convolutions whose blocks are whole output rows
+    for (unsigned n0 = 0; n0 < T.tile_w; n0 += bw) {
+        const unsigned rows_valid = min(bw, T.tile_w - n0);
         const bool row_ok = row < rows_valid;
         PixelWin pw = {0, 0, 0};
         const float *xr = nullptr;
@@ -453,7 +454,7 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                     } else if (tid == TMA_THREAD) {
                         if (!ps.dead && !mbar_wait(&sh->empty[s], ph ^ 1u, ctrl, status, 2)) ps.dead = true;
                         if (!ps.dead) {
-                            const unsigned bytes = (a_tma ? (a_kind == A_TMA_IM2COL ? rows_valid * 128u : A_STAGE_BYTES) : 0u) + (b_tma ? NB * 128u : 0u);
+                            const unsigned bytes = (a_tma ? (a_kind == A_TMA_IM2COL ? (bw != 128u ? bw : rows_valid) * 128u : A_STAGE_BYTES) : 0u) + (b_tma ? NB * 128u : 0u);
                             if (bytes) mbar_arrive_expect_tx(&sh->landed[s], bytes);
                             else mbar_arrive(&sh->landed[s]);
                             if (a_kind == A_TMA_ROWS) {
@@ -472,6 +473,13 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                             } else if (a_kind == A_TMA_IM2COL) {
                                 const unsigned tap = kc / L.IC, c0 = kc - tap * L.IC, kh = tap / L.KW, kw = tap - kh * L.KW;
                                 const unsigned hw = L.OH * L.OW;
+                                if (bw != 128u) {
+                                    // the block is whole output rows of one sample, or whole samples: one box
+                                    const unsigned n = T.pos_w + n0;
+                                    const unsigned b = n / hw, r = n - b * hw, oh = r / L.OW;
+                                    tma_load_4d(sA, (const unsigned char *)amap + (size_t)L.one_box * 128, (int)c0, (int)kw - (int)L.pad,
+                                                (int)(oh * L.stride + kh) - (int)L.pad, (int)b, &sh->landed[s]);
+                                } else
                                 #pragma unroll 1
                                 for (unsigned done = 0; done < rows_valid;) {
                                     const unsigned n = T.pos_w + n0 + done, rem = rows_valid - done;

@@ -121,8 +121,13 @@ def test_b200_tile_profile_only_changes_geometry(workdir):
     for i in range(a.num_ldata):
         ia, ib = a.ldata_info(i), b.ldata_info(i)
         assert (ia["H"], ia["W"]) == (ib["H"], ib["W"])
-        if ib["type"] == 2 and ib["W"] >= 128:        # conv tiles are whole 128-column blocks
-            assert ib["tile_w"] % 128 == 0
+        if ib["type"] == 2 and ib["W"] >= 128:
+            # conv tiles are whole blocks: 128 columns, or whole output rows / samples for the strided layers
+            # (OW = 28 -> 4 rows = 112, OW = 14 -> 7 rows = 98, 7 x 7 -> two samples = 98)
+            p = dnn.layer_params(i)
+            strided = p[api.STRIDE] > 1 and p[api.IN_C] % 32 == 0
+            block = {28: 112, 14: 98, 7: 98}[p[api.OUT_W]] if strided else 128
+            assert ib["tile_w"] % block == 0, (i, ib["tile_w"], block)
     # every tile has parents, parents precede children
     for t in range(b.ldata_info(0)["num_ninst"], b.num_ninst, 97):
         ps = b.parents(t)
