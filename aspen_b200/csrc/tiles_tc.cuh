@@ -544,7 +544,8 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                 float v[32];
                 if (op.softmax) {
                     // scores -> mask -> / sqrt(hd) -> exp, normalised by the column sum (ref src/tiled_kernels.c:859-876)
-                    const float scale = sqrtf((float)L.hd);
+                    // fast exponential and reciprocals: this path is the TF32 one, whose bound is 1e-2 of the layer's maximum
+                    const float inv_scale = 1.f / sqrtf((float)L.hd);
                     const unsigned q = op.q0 + n0 + row;
                     float sum = 0.f;
                     for (unsigned c = half; c < nchunk; c += 2) {
@@ -554,20 +555,21 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                             const unsigned m = ms + c * 32u + j;
                             if (m < T.tile_h) {
                                 float x = (L.masked && (T.pos_h + m) > q) ? -1e10f : v[j];
-                                sum += expf(x / scale);
+                                sum += __expf(x * inv_scale);
                             }
                         }
                     }
                     sh->partial[tid] = sum;
                     worker_barrier(NW);
                     sum = sh->partial[row] + sh->partial[row + 128u];
+                    const float inv_sum = 1.f / sum;
                     for (unsigned c = half; c < nchunk; c += 2) {
                         if (!ps.dead) tmem_ld32(tmem + (lane_base << 16) + c * 32u, v);
                         #pragma unroll
                         for (unsigned j = 0; j < 32; j++) {
                             const unsigned m = ms + c * 32u + j;
                             float x = (L.masked && (T.pos_h + m) > q) ? -1e10f : v[j];
-                            v[j] = store_round(expf(x / scale) / sum, L);
+                            v[j] = store_round(__expf(x * inv_scale) * inv_sum, L);
                         }
                         if (!ps.dead) store_block_coalesced(epi, v, oblk + c * 32u, L.ldc, n_valid, min(32u, cols_super - c * 32u));
                     }

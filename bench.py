@@ -39,7 +39,7 @@ TRAFFIC_BYTES = {"resnet50": 2.3e9}
 # Tiling of the nasm per workload: (row quantum, column quantum, min_ninst_per_ldata).  Tensor-core shaped
 # quanta; the values a graph computes do not depend on them.  Each is the best of a measured sweep
 # (quanta 64-256, min_ninst 100-592).
-TILING = {"resnet50": (128, 128, 148), "bert_base": (256, 128, 296)}
+TILING = {"resnet50": (128, 128, 180), "bert_base": (256, 128, 296)}
 
 
 def log(*a):

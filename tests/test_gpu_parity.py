@@ -105,12 +105,15 @@ def test_every_operand_staging_matches_oracle(env, workdir, monkeypatch):
 @pytest.mark.skipif(not ref.available(), reason="needs the reference build")
 @pytest.mark.parametrize("name,batch,seq", [("resnet50", 32, 0), ("bert_base", 32, 128)])
 def test_benchmark_configuration_matches_oracle(name, batch, seq, workdir):
-    """The benchmark's own workload (batch 32, B200 tile profile, TF32) against the reference."""
+    """The benchmark's own workload (batch 32, bench.py's tile quanta and min_ninst, TF32) against the reference."""
+    import bench
+    q_h, q_w, mn = bench.TILING[name]
     cfg, wf = harness.prepare(name, workdir)
-    dev = harness.Device(cfg, wf, batch, seq, 148, 0, 1)
+    api.lib().aspen_b200_set_tile_quanta(q_h, q_w, 100000000)
+    dev = harness.Device(cfg, wf, batch, seq, mn, 0, 2)      # profile 2: keep the quanta just set
     x = harness.make_input(name, dev.input_shape())
     assert dev.run(x) == 0, api.last_error()
-    outs = oracle_layers(name, cfg, wf, batch, seq, 148, x)
+    outs = oracle_layers(name, cfg, wf, batch, seq, mn, x)
     worst = check_layers(dev, outs, 0, name)
     assert worst < TF32_NORM
     dev.close()
