@@ -35,7 +35,7 @@ aspen_b200_last_error aspen_b200_group_status aspen_b200_set_tile_profile aspen_
 aspen_b200_set_precision aspen_b200_set_device aspen_b200_dnn_num_layers aspen_b200_dnn_layer_params
 aspen_b200_dnn_layer_type aspen_b200_nasm_num_ldata aspen_b200_nasm_num_ninst aspen_b200_nasm_total_flops
 aspen_b200_nasm_ldata_info aspen_b200_nasm_ninst_info aspen_b200_nasm_ninst_parents aspen_b200_nasm_ninst_children
-aspen_b200_nasm_get_ldata_packed aspen_b200_group_time_runs aspen_b200_group_profile aspen_b200_matmul_noalloc""".split()
+aspen_b200_nasm_get_ldata_packed aspen_b200_group_time_runs aspen_b200_group_profile aspen_b200_generate_nasm aspen_b200_matmul_noalloc""".split()
 
 
 def lib():
@@ -76,6 +76,7 @@ def lib():
         "aspen_b200_nasm_get_ldata_packed": (C.c_long, [vp, u, vp]),
         "aspen_b200_group_time_runs": (C.c_double, [vp, u, u, C.POINTER(C.c_ulonglong)]),
         "aspen_b200_group_profile": (i, [vp, vp, C.POINTER(u)]),
+        "aspen_b200_generate_nasm": (vp, [vp, u, u, C.POINTER(u)]),
         "aspen_b200_matmul_noalloc": (i, [vp, vp, vp, vp, u, u, u, i, vp]),
     }
     for name, (res, args) in sig.items():
@@ -129,6 +130,15 @@ class Nasm:
             self.h = L.apu_create_nasm(dnn.h, min_ninst, batch)
         if not self.h:
             raise RuntimeError("nasm creation failed: " + last_error())
+
+    @classmethod
+    def tuned(cls, dnn: Dnn, batch: int, seq: int = 0):
+        """aspen_b200_generate_nasm: tile-shape search on the device.  Returns (nasm, (row quantum, column quantum, min_ninst))."""
+        chosen = (C.c_uint * 3)()
+        h = lib().aspen_b200_generate_nasm(dnn.h, batch, seq, chosen)
+        if not h:
+            raise RuntimeError("aspen_b200_generate_nasm failed: " + last_error())
+        return cls(dnn, 0, handle=h), tuple(chosen)
 
     @classmethod
     def load(cls, dnn: Dnn, path: str) -> "Nasm":

@@ -332,6 +332,32 @@ static nasm_t *generate(aspen_dnn_t *dnn, unsigned int batch, unsigned int seq, 
     return make(best_num);
 }
 
+// Tile-shape search for this GPU: the reference tunes one number (tiles per layer) for its CPU kernels; here the
+// candidates are tensor-core shaped quanta (rows x columns of whole MMA blocks) times a tile count per layer, each
+// timed on the device with the scheduler kernel itself.  Values do not depend on the outcome.
+extern "C" nasm_t *aspen_b200_generate_nasm(aspen_dnn_t *dnn, unsigned int batch_size, unsigned int seq_num, unsigned int *chosen) {
+    if (!dnn || batch_size == 0) { ASPEN_ERR("aspen_b200_generate_nasm: no dnn or empty batch\n"); return nullptr; }
+    static const unsigned int quanta[][2] = {{128, 128}, {256, 128}, {128, 256}};
+    static const unsigned int counts[] = {100, 148, 180, 222, 296};
+    const TileQuanta saved = g_quanta;
+    double best = -1;
+    unsigned int best_q = 0, best_n = counts[1];
+    for (unsigned int q = 0; q < 3; q++)
+        for (unsigned int n : counts) {
+            aspen_b200_set_tile_quanta(quanta[q][0], quanta[q][1], saved.flop_per_ninst);
+            nasm_t *cand = seq_num ? apu_create_transformer_nasm(dnn, n, batch_size, seq_num) : apu_create_nasm(dnn, n, batch_size);
+            if (!cand) continue;
+            const double t = time_nasm_ms(cand, 8);
+            apu_destroy_nasm(cand);
+            if (t > 0 && (best < 0 || t < best)) { best = t; best_q = q; best_n = n; }
+        }
+    aspen_b200_set_tile_quanta(quanta[best_q][0], quanta[best_q][1], saved.flop_per_ninst);
+    nasm_t *out = seq_num ? apu_create_transformer_nasm(dnn, best_n, batch_size, seq_num) : apu_create_nasm(dnn, best_n, batch_size);
+    g_quanta = saved;
+    if (chosen) { chosen[0] = quanta[best_q][0]; chosen[1] = quanta[best_q][1]; chosen[2] = best_n; }
+    return out;
+}
+
 extern "C" nasm_t *apu_generate_nasm(aspen_dnn_t *dnn, unsigned int batch_size, unsigned int num_iter) {
     return generate(dnn, batch_size, 0, num_iter);
 }

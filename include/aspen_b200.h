@@ -165,6 +165,13 @@ int aspen_b200_group_status(dse_group_t *dse_group);
 void aspen_b200_set_tile_profile(int profile);
 void aspen_b200_set_tile_quanta(unsigned int h_min, unsigned int w_min, unsigned int flop_per_ninst);
 
+/* Tile-shape search for the GPU at hand (the B200 counterpart of apu_generate_nasm, ref src/apu_nasm.c:578-679,
+ * which tunes the tile count for the CPU kernels): tries tensor-core shaped quanta (128 x 128, 256 x 128,
+ * 128 x 256) times 100 ... 296 tiles per layer, times each candidate on the device, and returns a nasm built
+ * with the fastest.  seq_num = 0 for image networks.  chosen (may be NULL) receives {row quantum, column
+ * quantum, min_ninst_per_ldata}.  The global tile profile is left as it was.  Needs an sm_100 GPU. */
+nasm_t *aspen_b200_generate_nasm(aspen_dnn_t *dnn, unsigned int batch_size, unsigned int seq_num, unsigned int *chosen);
+
 /* Arithmetic of the contraction tiles for dse groups created afterwards:
  * 0 = TF32 operands on tcgen05 tensor cores, fp32 accumulate (default);
  * 1 = fp32 FFMA validation mode. */

@@ -335,3 +335,26 @@ def test_two_graphs_in_flight_upload_and_download_overlap_a_run(workdir):
         assert np.array_equal(a, b)
     assert not np.array_equal(want[0], want[1])
     group.close(); pair[1].close(); pair[0].close(); rpool.close(); dnn.close()
+
+
+def test_tile_shape_search_returns_a_working_graph(workdir):
+    """aspen_b200_generate_nasm times tensor-core shaped tilings on the device and returns the fastest; whatever it
+    picks, the values are the ones of a default graph (up to TF32 summation order of the input convolution)."""
+    cfg, wf = harness.prepare("tiny_cnn", workdir)
+    dnn = api.Dnn(cfg, wf)
+    tuned, chosen = api.Nasm.tuned(dnn, 6)
+    assert chosen[0] in (128, 256) and chosen[1] in (128, 256) and chosen[2] in (100, 148, 180, 222, 296)
+    plain = api.Nasm(dnn, 6, 0, 20)
+    rpool = api.Rpool()
+    group = api.DseGroup(0, 0)
+    group.set_rpool(rpool)
+    i0 = plain.ldata_info(0)
+    x = np.random.default_rng(5).standard_normal((i0["W"], i0["H"]), dtype=np.float32)
+    outs = []
+    for n_ in (tuned, plain):
+        rpool.add(n_, x); group.run(); group.wait(n_); group.stop()
+        assert group.status() == 0
+        outs.append(n_.ldata(n_.num_ldata - 1).copy())
+    assert outs[0].shape == outs[1].shape
+    assert np.abs(outs[0] - outs[1]).max() <= 2e-3 * np.abs(outs[1]).max()
+    group.close(); plain.close(); tuned.close(); rpool.close(); dnn.close()
