@@ -61,9 +61,11 @@ struct NasmDev {
     const unsigned *layer_tiles;     // [n_layers]
     const unsigned *init_ready;      // local ids of tiles runnable right after arming
     unsigned *layers_completed;      // single counter
+    const unsigned *layer_done_init; // [n_layers] tiles that count as complete when armed (layer 0: all; bypassed tiles)
+    unsigned layers_done_init;       // layers complete when armed
     volatile unsigned *completed;    // mapped host flag, set when every layer is complete
     const void *wmaps;               // CUtensorMap[]
-    unsigned n_tiles, n_layers, n_init, n_input_tiles;
+    unsigned n_tiles, n_layers, n_init, n_input_tiles;   // n_input_tiles: every tile complete when armed (input + bypassed)
     unsigned tile_base;              // global id of local tile 0 in this run
     unsigned queue_base;             // where this graph's initial ready tiles go in the queue
 };

@@ -186,7 +186,7 @@ struct DeviceNasm {
     LayerDev *layers = nullptr;
     TileDev *tiles = nullptr;
     unsigned *children = nullptr, *dep = nullptr, *dep_init = nullptr, *layer_done = nullptr, *layer_tiles = nullptr, *init_ready = nullptr;
-    unsigned *layers_completed = nullptr;
+    unsigned *layers_completed = nullptr, *layer_done_init = nullptr;
     unsigned *completed_h = nullptr, *completed_d = nullptr;   // mapped flag
     void *wmaps = nullptr;
     NasmDev host;        // template; tile_base / queue_base are filled per run
@@ -409,7 +409,7 @@ static void free_device_nasm(DeviceNasm *dn) {
     if (!dn) return;
     cudaFree(dn->arena); cudaFree(dn->layers); cudaFree(dn->tiles); cudaFree(dn->children); cudaFree(dn->dep);
     cudaFree(dn->dep_init); cudaFree(dn->layer_done); cudaFree(dn->layer_tiles); cudaFree(dn->init_ready);
-    cudaFree(dn->layers_completed); cudaFree(dn->wmaps);
+    cudaFree(dn->layers_completed); cudaFree(dn->layer_done_init); cudaFree(dn->wmaps);
     if (dn->completed_h) cudaFreeHost(dn->completed_h);
     cudaFree(dn->in_stage); cudaFree(dn->res_packed); cudaFree(dn->padded_in);
     if (dn->in_consumed) cudaEventDestroy(dn->in_consumed);
@@ -681,8 +681,42 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
             kids[t].push_back(child);
         }
         if (t >= n_input && T.need == 0) { ASPEN_ERR("tile %u of layer %u has no parents and can never run\n", t, T.layer); return -1; }
-        if (t >= n_input && dep_init[t] == T.need) init_ready.push_back(t);
     }
+    // Tiles whose values their parents write (fused residual layers) are taken out of the device graph: each of their
+    // parent edges is replaced by edges to their children, and they count as complete from the start.  Without this
+    // every such tile costs a pass through the ready queue and a completion on some CTA.  ASPEN_B200_KEEP_NOOP_TILES=1
+    // leaves them in (the scheduler then completes them when they become ready).
+    std::vector<unsigned> layer_done_init(nasm->num_ldata, 0);
+    layer_done_init[0] = n_input;
+    unsigned n_bypassed = 0;
+    const char *keep_noop = getenv("ASPEN_B200_KEEP_NOOP_TILES");
+    if (!(keep_noop && atoi(keep_noop) != 0)) {
+        std::vector<std::vector<unsigned>> pars(n);
+        for (unsigned p = 0; p < n; p++)
+            for (unsigned c : kids[p]) pars[c].push_back(p);
+        for (unsigned t = n_input; t < n; t++) {
+            if (!(tiles[t].flags & TILE_WRITTEN_BY_PARENTS) || pars[t].empty() || pars[t].size() != tiles[t].need) continue;
+            bool input_parent = false;
+            for (unsigned p : pars[t]) input_parent |= p < n_input;
+            if (input_parent) continue;
+            for (unsigned c : kids[t]) {                       // one edge t -> c becomes the edges p -> c
+                tiles[c].need += (unsigned)pars[t].size() - 1u;
+                auto it = std::find(pars[c].begin(), pars[c].end(), t);
+                if (it != pars[c].end()) pars[c].erase(it);
+                for (unsigned p : pars[t]) { kids[p].push_back(c); pars[c].push_back(p); }
+            }
+            for (unsigned p : pars[t]) kids[p].erase(std::remove(kids[p].begin(), kids[p].end(), t), kids[p].end());
+            kids[t].clear();
+            pars[t].clear();
+            tiles[t].need = 0xffffffffu;                       // never reached
+            layer_done_init[tiles[t].layer]++;
+            n_bypassed++;
+        }
+    }
+    unsigned layers_done_init = 0;
+    for (unsigned i = 0; i < nasm->num_ldata; i++) layers_done_init += layer_done_init[i] == nasm->ldata[i].num_ninst ? 1u : 0u;
+    for (unsigned t = n_input; t < n; t++)
+        if (tiles[t].need != 0xffffffffu && dep_init[t] == tiles[t].need) init_ready.push_back(t);
     std::vector<unsigned> children;   // pairs: (child tile, count that child waits for)
     for (unsigned t = 0; t < n; t++) {
         tiles[t].child_off = (unsigned)(children.size() / 2);
@@ -692,7 +726,8 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
     for (unsigned i = 0; i < nasm->num_ldata; i++) layer_tiles[i] = nasm->ldata[i].num_ninst;
     std::vector<unsigned> zeros(std::max(n, nasm->num_ldata), 0);
     if (to_device(&dn->tiles, tiles) != 0 || to_device(&dn->children, children) != 0 || to_device(&dn->dep_init, dep_init) != 0 ||
-        to_device(&dn->init_ready, init_ready) != 0 || to_device(&dn->layer_tiles, layer_tiles) != 0)
+        to_device(&dn->init_ready, init_ready) != 0 || to_device(&dn->layer_tiles, layer_tiles) != 0 ||
+        to_device(&dn->layer_done_init, layer_done_init) != 0)
         return -1;
     CUDA_TRY(cudaMalloc(&dn->dep, std::max<size_t>(n, 1) * sizeof(unsigned)));
     CUDA_TRY(cudaMalloc(&dn->layer_done, nasm->num_ldata * sizeof(unsigned)));
@@ -715,7 +750,8 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
     H.layers = dn->layers; H.tiles = dn->tiles; H.children = dn->children; H.dep = dn->dep; H.dep_init = dn->dep_init;
     H.layer_done = dn->layer_done; H.layer_tiles = dn->layer_tiles; H.init_ready = dn->init_ready;
     H.layers_completed = dn->layers_completed; H.completed = dn->completed_d; H.wmaps = dn->wmaps;
-    H.n_tiles = n; H.n_layers = nasm->num_ldata; H.n_init = (unsigned)init_ready.size(); H.n_input_tiles = n_input;
+    H.n_tiles = n; H.n_layers = nasm->num_ldata; H.n_init = (unsigned)init_ready.size(); H.n_input_tiles = n_input + n_bypassed;
+    H.layer_done_init = dn->layer_done_init; H.layers_done_init = layers_done_init;
     return 0;
 }
 

@@ -113,8 +113,8 @@ static __global__ void arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue
     for (unsigned g = 0; g < n_nasm; g++) {
         const NasmDev G = nasms[g];
         for (unsigned i = t0; i < G.n_tiles; i += stride) G.dep[i] = G.dep_init[i];
-        for (unsigned i = t0; i < G.n_layers; i += stride) G.layer_done[i] = i == 0 ? G.layer_tiles[0] : 0u;
-        if (t0 == 0) { *G.layers_completed = 1u; *G.completed = 0u; }
+        for (unsigned i = t0; i < G.n_layers; i += stride) G.layer_done[i] = G.layer_done_init[i];
+        if (t0 == 0) { *G.layers_completed = G.layers_done_init; *G.completed = 0u; }
     }
     if (t0 == 0) {
         ctrl->head = 0u; ctrl->tail = n_init_total; ctrl->done = n_input_total; ctrl->total = total; ctrl->cap = total;
