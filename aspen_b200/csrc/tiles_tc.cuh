@@ -11,12 +11,15 @@
 // Staging.  Both operands are K-major, 32 fp32 (128 bytes) per row and k-chunk, in the 128-byte
 // swizzled shared-memory layout UMMA descriptors and TMA share:
 //     byte(row r, 16-byte piece c) = r * 128 + ((c ^ (r & 7)) << 4),   stage base 1024-byte aligned.
-// Weights arrive by TMA (one 64-row box per 8 KB) straight from the [rows][Kpad] device copy.
-// Activations are gathered by the worker threads with cp.async (zero-fill for padding taps and
-// k >= K) -- this is the im2col-free part: a conv tile reads pixel (b, oh*s+kh-p, ow*s+kw-p)
-// directly from the NHWC parent matrix.  cp.async writes go through the generic proxy, so a
-// thread waits for its own copies, issues fence.proxy.async and only then arrives on the stage's
-// "full" mbarrier, two stages behind its newest copy.
+// Weights arrive by TMA (64-row boxes) straight from the [rows][Kpad] device copy.  Activations arrive
+// by TMA wherever the access pattern is a box of the parent matrix -- plain 2-D boxes, a shifted box
+// with a zero fix-up of the rows whose tap leaves the image, strided 3-D / 4-D boxes for the stem and the
+// stride-2 layers (the table before `enum { A_GATHER ...` lists the kinds) -- and only otherwise are
+// gathered by the worker threads with cp.async (zero-fill for padding taps and k >= K).  None of
+// them materialises an im2col matrix: a conv tile reads pixel (b, oh*s+kh-p, ow*s+kw-p) of the NHWC
+// parent directly.  cp.async writes go through the generic proxy, so a thread waits for its own
+// copies, issues fence.proxy.async and only then arrives on the stage's "full" mbarrier, two stages
+// behind its newest copy.
 //
 // Roles in the CTA: NW worker threads (gather + epilogue), one TMA thread, one MMA thread.
 // Every wait is bounded: when a spin budget runs out the thread records an error, raises the
