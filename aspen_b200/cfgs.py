@@ -165,6 +165,50 @@ def tiny_cnn():
     return c.text(), c.weighted
 
 
+YOLO_ANCHORS = "10,13,  16,30,  33,23,  30,61,  62,45,  59,119,  116,90,  156,198,  373,326"
+
+
+def tiny_yolo(classes: int = 3):
+    """Two detection heads joined by an upsample-and-concatenate layer, in the vocabulary of the
+    reference's files/yolov3/yolov3_aspen.cfg: `[yolo]` (mask / anchors / classes / stride),
+    `[convolutional] parent=-4` branching off before the first head, `[append] stride=2 parent=-1 from=-7`."""
+    c = _Cfg()
+    c.sec("net", height=32, width=32, channels=3)
+    head = 3 * (5 + classes)
+    _conv(c, 3, 16, 3, 1, 1, "leaky", bn=False)          # 1  32 x 32
+    _conv(c, 16, 32, 3, 2, 1, "leaky", bn=False)         # 2  16 x 16
+    _conv(c, 32, 32, 1, 1, 0, "leaky", bn=False)         # 3  16 x 16, joined again by the append layer
+    _conv(c, 32, 64, 3, 2, 1, "leaky", bn=False)         # 4  8 x 8
+    _conv(c, 64, 32, 1, 1, 0, "leaky", bn=False)         # 5
+    _conv(c, 32, 64, 3, 1, 1, "leaky", bn=False)         # 6
+    _conv(c, 64, head, 1, 1, 0, "linear", bn=False)      # 7
+    c.sec("yolo", mask="6,7,8", stride=4, anchors=YOLO_ANCHORS, classes=classes, num=9)     # 8
+    _conv(c, 32, 16, 1, 1, 0, "leaky", parent=-4, bn=False)                                 # 9  from layer 5
+    c.sec("append", stride=2, parent=-1, **{"from": -7})                                    # 10 16 x 16, 16 + 32 channels
+    _conv(c, 48, 32, 3, 1, 1, "leaky", bn=False)         # 11
+    _conv(c, 32, head, 1, 1, 0, "linear", bn=False)      # 12
+    c.sec("yolo", mask="3,4,5", stride=2, anchors=YOLO_ANCHORS, classes=classes, num=9)     # 13
+    return c.text(), c.weighted
+
+
+def tiny_acts():
+    """Every activation of the cfg dialect that the benchmark networks do not use -- `logistic`, `tanh`, `elu`,
+    `selu` (reference src/naive_kernels.c:11-57) -- once on a convolution / connected epilogue and once on a
+    residual or pooling tile."""
+    c = _Cfg()
+    c.sec("net", height=12, width=12, channels=4)
+    _conv(c, 4, 32, 3, 1, 1, "logistic", bn=False)       # 1
+    _conv(c, 32, 32, 1, 1, 0, "tanh", bn=False)          # 2
+    _conv(c, 32, 32, 3, 1, 1, "elu", bn=False)           # 3
+    c.sec("shortcut", **{"from": -3}, activation="selu") # 4
+    _conv(c, 32, 64, 3, 2, 1, "selu", bn=False)          # 5  6 x 6
+    c.sec("maxpool", size=2, stride=2, activation="tanh")# 6  3 x 3
+    c.sec("avgpool", size=3, stride=1, activation="elu") # 7  1 x 1
+    c.sec("connected", output=16, activation="logistic") # 8
+    c.weighted.append(("fc", (16, 64, 1, 1), 64))
+    return c.text(), c.weighted
+
+
 def tiny_transformer(masked: bool = False, pre_ln: bool = False):
     return transformer(2, 64, 4, 128, pre_ln=pre_ln, masked=masked, act="gelu_acc" if masked else "gelu")
 
@@ -177,6 +221,8 @@ BUILDERS = {
     "gpt2_124M": gpt2_124m,
     "tiny_cnn": tiny_cnn,
     "tiny_transformer": tiny_transformer,
+    "tiny_yolo": tiny_yolo,
+    "tiny_acts": tiny_acts,
 }
 
 

@@ -35,6 +35,10 @@ extern "C" int aspen_b200_set_device(int device) {
 
 int engine_current_device() {
     if (g_device >= 0) return g_device;
+    if (const char *v = getenv("ASPEN_B200_DEVICE")) {     // for callers that cannot call aspen_b200_set_device
+        int n = 0, want = atoi(v);
+        if (*v && cudaGetDeviceCount(&n) == cudaSuccess && want >= 0 && want < n) return want;
+    }
     int d = 0;
     if (cudaGetDevice(&d) != cudaSuccess) return 0;
     return d;

@@ -1,9 +1,8 @@
 // aspen_b200_matmul_noalloc: one matmul layer run as a tile graph by the persistent scheduler
 // kernel, for callers that must not allocate.
 //
-// Who cannot allocate: code that runs between cudaStreamBeginCapture and EndCapture of somebody
-// else's graph, plug-ins that are handed a fixed memory budget by their host framework (a serving
-// runtime that pre-sizes every pool at start-up and treats a later cudaMalloc as a bug), and
+// Who cannot allocate: plug-ins that are handed a fixed memory budget by their host framework (a
+// serving runtime that pre-sizes every pool at start-up and treats a later cudaMalloc as a bug), and
 // latency-critical loops where the implicit device synchronisation of cudaMalloc / cudaFree is not
 // acceptable.  The regular API builds a device image per nasm (arena, descriptors, counters, queue)
 // with cudaMalloc; this entry point keeps everything the scheduler needs besides the caller's own
@@ -15,7 +14,8 @@
 //     set-up kernel rewrites all of it that a run reads (counters and queue start from zero again);
 //     two calls that overlap on the GPU (different streams, or different host threads) race;
 //   * the first call on a device looks the array's address up (cudaGetSymbolAddress) -- make that
-//     call before any stream capture.
+//     call before any stream capture;
+//   * every call ends by reading the scheduler's status back and synchronising its stream.
 #include "internal.h"
 #include "scheduler.cuh"
 
@@ -107,7 +107,8 @@ extern "C" int aspen_b200_matmul_noalloc(const float *x_dev, const float *w_dev,
         return -1;
     }
     if (activation < 0 || activation >= NUM_ACTIVATIONS) { ASPEN_ERR("aspen_b200_matmul_noalloc: unknown activation %d\n", activation); return -1; }
-    const unsigned long long tiles = (unsigned long long)((m + NOALLOC_TILE - 1) / NOALLOC_TILE) * ((n_cols + NOALLOC_TILE - 1) / NOALLOC_TILE);
+    // 64-bit: m or n_cols close to 2^32 must not wrap into a small tile count
+    const unsigned long long tiles = (((unsigned long long)m + NOALLOC_TILE - 1) / NOALLOC_TILE) * (((unsigned long long)n_cols + NOALLOC_TILE - 1) / NOALLOC_TILE);
     if (tiles > NOALLOC_MAX_TILES) {
         ASPEN_ERR("aspen_b200_matmul_noalloc: %u x %u outputs need %llu tiles of 128 x 128; the fixed scratch array holds %u. "
                   "Use the regular API (it allocates) for larger layers.\n", m, n_cols, tiles, NOALLOC_MAX_TILES);

@@ -6,9 +6,17 @@
 
 #include <fstream>
 
-static thread_local int g_precision = 0;
+// -1: not set by the program.  A caller that cannot be changed (a program written against the reference's
+// header) picks the mode with the environment: ASPEN_B200_PRECISION=fp32 (or 1) selects the FFMA validation mode.
+static thread_local int g_precision = -1;
 
 extern "C" void aspen_b200_set_precision(int mode) { g_precision = mode ? 1 : 0; }
+
+static int effective_precision() {
+    if (g_precision >= 0) return g_precision;
+    const char *v = getenv("ASPEN_B200_PRECISION");
+    return (v && (!strcmp(v, "fp32") || !strcmp(v, "1"))) ? 1 : 0;
+}
 
 // ---- rpool -----------------------------------------------------------------------------------
 extern "C" rpool_t *rpool_init(void) { return new rpool_t(); }
@@ -99,7 +107,7 @@ extern "C" void rpool_reset_nasm(rpool_t *rpool, nasm_t *nasm) {
 extern "C" dse_group_t *dse_group_init(unsigned int num_dse) {
     dse_group_t *g = new dse_group_t();
     g->num_dses = num_dse;
-    g->precision = g_precision;
+    g->precision = effective_precision();
     g->device = engine_current_device();
     g->engine = engine_create(g->device, g->precision, num_dse);
     if (!g->engine) {

@@ -215,9 +215,9 @@ int aspen_b200_group_profile(dse_group_t *dse_group, unsigned long long *out, un
 /* No counterpart in the reference.  One matmul layer, out[n][m] = act(bias[m] + sum_k w[m][k] * x[n][k])
  * in fp32 FMA arithmetic, run as 128 x 128 tiles by the same persistent scheduler kernel as every
  * other call -- but WITHOUT ALLOCATING ANYTHING.  It is for callers that are not allowed to call
- * cudaMalloc: code running inside another party's stream capture, plug-ins of a serving runtime that
- * fixes all memory pools at start-up, loops that cannot afford the device-wide synchronisation an
- * allocation implies.  All pointers are DEVICE pointers the caller owns: x [n_cols][k], w [m][k],
+ * cudaMalloc: plug-ins of a serving runtime that fixes all memory pools at start-up and treats a later
+ * allocation as a bug, and loops that cannot afford the device-wide synchronisation an allocation
+ * implies.  All pointers are DEVICE pointers the caller owns: x [n_cols][k], w [m][k],
  * bias [m] or NULL, out [n_cols][m], rows contiguous; cuda_stream is a cudaStream_t (NULL = default).
  * Everything else the scheduler needs (tile descriptors, ready queue, counters, status) lives in one
  * fixed array in device memory that every GPU holds from the moment the library is loaded until exit
@@ -229,7 +229,8 @@ int aspen_b200_group_profile(dse_group_t *dse_group, unsigned long long *out, un
  *     -- two streams, two host threads -- corrupt each other.  Serialise them;
  *   - the first call on a device resolves the array's device address; make that call before any
  *     stream capture begins.
- * The call returns after the work has finished.  Returns 0, -1 bad arguments, -2 too large, -3 CUDA
+ * The call waits for its own work on `cuda_stream` (it synchronises that stream to read the scheduler's
+ * status back) and returns after the work has finished.  Returns 0, -1 bad arguments, -2 too large, -3 CUDA
  * error, -4 the scheduler reported an error (see aspen_b200_last_error). */
 #define ASPEN_B200_NOALLOC_MAX_TILES 4096
 int aspen_b200_matmul_noalloc(const float *x_dev, const float *w_dev, const float *bias_dev, float *out_dev,

@@ -234,3 +234,39 @@ void oracle_v_attention(const float *p, const float *v, float *out, int B, int S
                 out[(size_t)(b * S + n) * hidden + m] = acc;
             }
 }
+
+/* ref src/tiled_kernels.c:675-709: box decode of one detection head.  in: [B*IH*IW][a_num * C] (C = classes + 5),
+ * out: [B * a_num * IH * IW][C], column b*(a_num*IH*IW) + a*(IH*IW) + h*IW + w.
+ *   x = (sigmoid(in0) + w) * stride,  y = (sigmoid(in1) + h) * stride,
+ *   bw = exp(in2) * anchor[2a],       bh = exp(in3) * anchor[2a+1],   the rest: sigmoid. */
+void oracle_yolo(const float *in, const float *anchors, float *out, int B, int IH, int IW, int IC, int C, int stride)
+{
+    const int a_num = IC / C, hw = IH * IW;
+    for (int b = 0; b < B; b++)
+        for (int a = 0; a < a_num; a++)
+            for (int h = 0; h < IH; h++)
+                for (int w = 0; w < IW; w++) {
+                    const float *x = in + ((size_t)(b * hw) + h * IW + w) * IC + a * C;
+                    float *o = out + ((size_t)(b * a_num + a) * hw + h * IW + w) * C;
+                    o[0] = (1.0f / (1.0f + expf(-x[0])) + w) * stride;
+                    o[1] = (1.0f / (1.0f + expf(-x[1])) + h) * stride;
+                    o[2] = expf(x[2]) * anchors[2 * a];
+                    o[3] = expf(x[3]) * anchors[2 * a + 1];
+                    for (int j = 4; j < C; j++) o[j] = 1.0f / (1.0f + expf(-x[j]));
+                }
+}
+
+/* ref src/tiled_kernels.c:711-741: PARENT_0 ([B*IH*IW][C1]) upsampled by `stride` (nearest neighbour), then
+ * PARENT_1's channels ([B*OH*OW][C2], OH = IH*stride) behind it: out [B*OH*OW][C1 + C2]. */
+void oracle_append(const float *in1, const float *in2, float *out, int B, int IH, int IW, int C1, int C2, int stride)
+{
+    const int OH = IH * stride, OW = IW * stride;
+    for (int b = 0; b < B; b++)
+        for (int h = 0; h < OH; h++)
+            for (int w = 0; w < OW; w++) {
+                const size_t col = ((size_t)b * OH + h) * OW + w;
+                float *o = out + col * (C1 + C2);
+                memcpy(o, in1 + (((size_t)b * IH + h / stride) * IW + w / stride) * C1, (size_t)C1 * sizeof(float));
+                memcpy(o + C1, in2 + col * C2, (size_t)C2 * sizeof(float));
+            }
+}

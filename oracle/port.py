@@ -23,7 +23,7 @@ ACT = {None: 0, "logistic": 1, "linear": 0, "none": 0, "tanh": 3, "relu": 4, "le
 TYPE = {"[net]": "input", "[network]": "input", "[conv]": "conv", "[convolutional]": "conv", "[shortcut]": "residual",
         "[max]": "maxpool", "[maxpool]": "maxpool", "[avg]": "avgpool", "[avgpool]": "avgpool", "[conn]": "fc",
         "[connected]": "fc", "[soft]": "softmax", "[softmax]": "softmax", "[matmul]": "matmul",
-        "[attention_k]": "attn_k", "[attention_v]": "attn_v", "[layernorm]": "layernorm"}
+        "[attention_k]": "attn_k", "[attention_v]": "attn_v", "[layernorm]": "layernorm", "[yolo]": "yolo", "[append]": "append"}
 
 
 def build() -> str:
@@ -144,6 +144,23 @@ def run(cfg_text: str, weight_list, x: np.ndarray, batch: int, seq: int = 0):
             out = np.empty((batch * seq, hidden), np.float32)
             L.oracle_v_attention(_p(p), _p(v), _p(out), batch, seq, heads, hidden)
             sh = {"M": hidden}
+        elif t == "yolo":
+            ps = shapes[par]
+            c = geti("classes") + 5
+            # anchors of the three masked boxes (reference src/darknet_parser.c:487-549)
+            masks = [int(v) for v in o["mask"].split(",")]
+            allanch = [float(v) for v in o["anchors"].split(",")]
+            anch = np.array([allanch[2 * m + j] for m in masks[:3] for j in (0, 1)], np.float32)
+            a_num = ps["C"] // c
+            out = np.empty((batch * a_num * ps["H"] * ps["W"], c), np.float32)
+            L.oracle_yolo(_p(outs[par]), _p(anch), _p(out), batch, ps["H"], ps["W"], ps["C"], c, geti("stride"))
+            sh = {"C": c, "H": 1, "W": ps["H"] * ps["W"] * a_num}
+        elif t == "append":
+            ps, ps2 = shapes[par], shapes[frm]
+            s = geti("stride") or 1
+            out = np.empty((batch * ps["H"] * s * ps["W"] * s, ps["C"] + ps2["C"]), np.float32)
+            L.oracle_append(_p(outs[par]), _p(outs[frm]), _p(out), batch, ps["H"], ps["W"], ps["C"], ps2["C"], s)
+            sh = {"C": ps["C"] + ps2["C"], "H": ps["H"] * s, "W": ps["W"] * s}
         else:
             raise ValueError(t)
         outs.append(out)

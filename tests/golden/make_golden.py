@@ -1,7 +1,7 @@
 """Generates the committed fixtures under tests/golden/ by running the UNMODIFIED reference
 (oracle/_ref/libaspen_ref.so, built from the reference sources by oracle/Makefile).
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [net ...]      (no names: every fixture)
 
 Inputs and weights are seeded (tests/harness.py), so only outputs are stored:
   values_<net>.npz   reference layer-walk activations (final layer + a few hidden layers)
@@ -23,8 +23,9 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 import harness  # noqa: E402
 from oracle import ref  # noqa: E402
 
-VALUE_CASES = [("tiny_cnn", 2, 0, 20), ("tiny_transformer", 2, 16, 20), ("tiny_gpt", 2, 16, 20), ("custom", 2, 0, 50)]
-GRAPH_CASES = [("tiny_cnn", 2, 0, 20), ("tiny_transformer", 2, 16, 20), ("custom", 2, 0, 50), ("resnet50", 1, 0, 50),
+VALUE_CASES = [("tiny_cnn", 2, 0, 20), ("tiny_transformer", 2, 16, 20), ("tiny_gpt", 2, 16, 20), ("custom", 2, 0, 50),
+               ("tiny_yolo", 2, 0, 8), ("tiny_acts", 3, 0, 8)]
+GRAPH_CASES = [("tiny_yolo", 2, 0, 8), ("tiny_acts", 3, 0, 8), ("tiny_cnn", 2, 0, 20), ("tiny_transformer", 2, 16, 20), ("custom", 2, 0, 50), ("resnet50", 1, 0, 50),
                ("resnet50", 4, 0, 100), ("vgg16", 1, 0, 100), ("bert_base", 1, 32, 20), ("bert_base", 4, 128, 100),
                ("gpt2_124M", 2, 64, 50)]
 
@@ -39,7 +40,10 @@ def nasm_digest(path):
 
 def main():
     wd = tempfile.mkdtemp()
+    only = set(sys.argv[1:])
     for name, batch, seq, mn in VALUE_CASES:
+        if only and name not in only:
+            continue
         cfg, wf = harness.prepare(name, wd)
         rn = ref.RefNet(cfg, wf, batch, seq, min_ninst=mn)
         i0 = rn.ldata_info(0)
@@ -51,6 +55,8 @@ def main():
         rn.close()
         print("values", name, {k: v.shape for k, v in arrays.items()})
     for name, batch, seq, mn in GRAPH_CASES:
+        if only and name not in only:
+            continue
         cfg, _ = harness.prepare(name, wd)
         rn = ref.RefNet(cfg, None, batch, seq, min_ninst=mn, with_parents=True)
         out = os.path.join(wd, "g.nasm")

@@ -14,6 +14,8 @@ NETS = {
     "tiny_transformer": ({}, "n002", (13, 12)),
     "tiny_gpt": ({"masked": True, "pre_ln": True}, "n002", (15, 14)),
     "custom": ({}, "he", (5, 6)),
+    "tiny_yolo": ({}, "he", (17, 16)),
+    "tiny_acts": ({}, "he", (19, 18)),
     "resnet50": ({}, "he", (1, 0)),
     "vgg16": ({}, "he", (2, 2)),
     "bert_base": ({}, "n002", (3, 3)),

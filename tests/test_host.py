@@ -17,7 +17,7 @@ from oracle import ref
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 GOLDEN = os.path.join(ROOT, "tests", "golden")
-REFDIR = "/root/reference"
+REFDIR = os.environ.get("ASPEN_REFERENCE", "/root/reference")
 
 
 def _digest(path):
@@ -223,3 +223,103 @@ def test_engine_refuses_to_run_without_gpu():
         pytest.skip("GPU present")
     assert api.lib().dse_group_init(4) is None
     assert "CUDA" in api.last_error() or "device" in api.last_error()
+
+
+def _aspen_tensors(path):
+    """The raw tensors of a .aspen file, in file order (layout: reference src/apu_file_io.c:434-501)."""
+    blob = open(path, "rb").read()
+    out, pos = [], 0
+    while True:
+        start = blob.find(b"\t\tNUM_DIMS:", pos)
+        if start < 0:
+            return out
+        data = blob.find(b"\t\tTENSOR_DATA:\n", start)
+        head = blob[start:data].decode()
+        nd = int(re.search(r"NUM_DIMS:(\d+)", head).group(1))
+        order = [int(v) for v in re.findall(r"\t\t\t\d+ (\d+)\n", head.split("DATA_DIM_ORDER:")[1].split("DATA_DIM_ORDER_END")[0])]
+        dims = [int(v) for v in re.findall(r"\t\t\t\d+ (\d+)\n", head.split("TENSOR_DIMS:")[1].split("TENSOR_DIMS_END")[0])]
+        n = int(np.prod([dims[order[k]] for k in range(nd)]))
+        data += len(b"\t\tTENSOR_DATA:\n")
+        out.append(np.frombuffer(blob[data:data + 4 * n], np.float32))
+        assert blob[data + 4 * n:data + 4 * n + 18] == b"\t\tTENSOR_DATA_END\n"
+        pos = data + 4 * n
+
+
+def _bn_weight_file(path, tensors, bn):
+    """ASPEN_DATA file whose conv layers carry BN_VAR / BN_MEAN / BN_WEIGHT blocks next to WEIGHT and BIAS
+    (the writer side of reference examples/3. custom_example/custom_net.py; reader src/apu_file_io.c:135-140,346-413)."""
+    with open(path, "wb") as f:
+        f.write(b"ASPEN_DATA\n")
+        for i, (w, b) in enumerate(tensors, start=1):
+            blocks = [("WEIGHT", w), ("BIAS", b)]
+            if i in bn:
+                blocks += [("BN_VAR", bn[i][0]), ("BN_MEAN", bn[i][1]), ("BN_WEIGHT", bn[i][2])]
+            for name, arr in blocks:
+                raw = np.ascontiguousarray(arr, dtype="<f4").tobytes()
+                f.write(f"LAYER:{i}\nTENSOR_TYPE:{name}\nDATA_SIZE:{len(raw)}\nDATA_START:\n".encode() + raw + b"DATA_END\nLAYER_END\n")
+
+
+def test_batchnorm_is_folded_on_load_like_the_reference(workdir):
+    """Weight files may carry batch-norm statistics per convolution; both libraries fold them into weight and bias
+    while loading (reference src/apu_file_io.c:400-413, src/util.c:259-276: w *= g / sqrt(var + 1e-5),
+    b -= g * mean / sqrt(var + 1e-5))."""
+    from aspen_b200 import weights
+    kw, scheme, (wseed, _) = harness.NETS["tiny_cnn"]
+    text, wl = cfgs.BUILDERS["tiny_cnn"](**kw)
+    cfg = os.path.join(workdir, "bn.cfg")
+    open(cfg, "w").write(text)
+    tensors = weights.make_weights(wl, wseed, scheme)
+    rng = np.random.default_rng(23)
+    bn = {}
+    for i, (kind, shape, _) in enumerate(wl, start=1):
+        if kind == "conv" and i != 2:          # one convolution stays without statistics
+            n = shape[0]
+            bn[i] = (rng.uniform(0.5, 2.0, n).astype(np.float32), rng.standard_normal(n).astype(np.float32),
+                     rng.uniform(0.5, 1.5, n).astype(np.float32))
+    wf = os.path.join(workdir, "bn.bin")
+    _bn_weight_file(wf, tensors, bn)
+    L = api.lib()
+    dnn = api.Dnn(cfg, wf)
+    mine = os.path.join(workdir, "bn_mine.aspen")
+    L.apu_save_dnn_to_file(dnn.h, mine.encode())
+    dnn.close()
+    got = _aspen_tensors(mine)
+    # the same file without statistics gives the unfolded tensors in the same (packed) layout
+    plain = os.path.join(workdir, "bn_plain.bin")
+    weights.write_aspen_data(plain, tensors)
+    dnn = api.Dnn(cfg, plain)
+    base = os.path.join(workdir, "bn_base.aspen")
+    L.apu_save_dnn_to_file(dnn.h, base.encode())
+    dnn.close()
+    raw = _aspen_tensors(base)
+    assert len(got) == len(raw) == 2 * len(wl)
+    changed = 0
+    for i in range(1, len(wl) + 1):
+        w0, b0, w1, b1 = raw[2 * i - 2], raw[2 * i - 1], got[2 * i - 2], got[2 * i - 1]
+        if i not in bn:
+            assert np.array_equal(w0, w1) and np.array_equal(b0, b1)
+            continue
+        var, mean, g = bn[i]
+        inv = np.sqrt((var.astype(np.float64) + 1e-5).astype(np.float32))
+        np.testing.assert_allclose(b1, b0 - g * mean / inv, rtol=2e-6, atol=1e-7)
+        # packed weight layout [rows/8][K][8] (reference src/apu.c:14-40): element (r, k) at ((r // 8) * K + k) * 8 + r % 8
+        rows = len(b0)
+        k = w0.size // (8 * ((rows + 7) // 8))
+        scale = np.zeros(8 * ((rows + 7) // 8), np.float32)
+        scale[:rows] = g / inv
+        want = (w0.reshape(-1, k, 8) * scale.reshape(-1, 1, 8)).ravel()
+        np.testing.assert_allclose(w1, want, rtol=2e-6, atol=1e-9)
+        changed += 1
+    assert changed == len(bn) >= 4
+    if ref.available():
+        R = ref.lib()
+        R.apu_save_dnn_to_file.argtypes = [C.c_void_p, C.c_char_p]
+        rd = R.apu_create_dnn(cfg.encode(), wf.encode())
+        assert rd
+        theirs = os.path.join(workdir, "bn_ref.aspen")
+        R.apu_save_dnn_to_file(rd, theirs.encode())
+        R.apu_destroy_dnn(rd)
+        want = _aspen_tensors(theirs)
+        assert len(want) == len(got)
+        for a, b in zip(got, want):
+            np.testing.assert_allclose(a, b, rtol=2e-6, atol=1e-9)   # the reference is built with -Ofast: not bit-exact

@@ -11,7 +11,7 @@ from aspen_b200 import cfgs, weights
 from oracle import port, ref
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-CASES = [("tiny_cnn", 2, 0), ("tiny_transformer", 2, 16), ("tiny_gpt", 2, 16), ("custom", 2, 0)]
+CASES = [("tiny_cnn", 2, 0), ("tiny_transformer", 2, 16), ("tiny_gpt", 2, 16), ("custom", 2, 0), ("tiny_yolo", 2, 0), ("tiny_acts", 3, 0)]
 # The oracle sums in plain k order in fp32, the reference in 8-wide vectors over K-blocks of 368:
 # agreement is to rounding, not bit-exact.
 REL, ABS = 1e-4, 1e-5
@@ -49,7 +49,7 @@ def test_port_matches_reference_fixtures(name, batch, seq):
 
 
 @pytest.mark.skipif(not ref.available(), reason="reference build (oracle/_ref) not present")
-@pytest.mark.parametrize("name,batch,seq", [("tiny_cnn", 3, 0), ("tiny_gpt", 1, 24)])
+@pytest.mark.parametrize("name,batch,seq", [("tiny_cnn", 3, 0), ("tiny_gpt", 1, 24), ("tiny_yolo", 3, 0), ("tiny_acts", 2, 0)])
 def test_port_matches_reference_live(name, batch, seq, workdir):
     cfg, wf = harness.prepare(name, workdir)
     text, w = _net(name)
