@@ -35,7 +35,8 @@ aspen_b200_last_error aspen_b200_group_status aspen_b200_set_tile_profile aspen_
 aspen_b200_set_precision aspen_b200_set_device aspen_b200_dnn_num_layers aspen_b200_dnn_layer_params
 aspen_b200_dnn_layer_type aspen_b200_nasm_num_ldata aspen_b200_nasm_num_ninst aspen_b200_nasm_total_flops
 aspen_b200_nasm_ldata_info aspen_b200_nasm_ninst_info aspen_b200_nasm_ninst_parents aspen_b200_nasm_ninst_children
-aspen_b200_nasm_get_ldata_packed aspen_b200_group_time_runs aspen_b200_group_profile aspen_b200_generate_nasm aspen_b200_matmul_noalloc""".split()
+aspen_b200_nasm_get_ldata_packed aspen_b200_group_time_runs aspen_b200_group_profile aspen_b200_generate_nasm aspen_b200_set_hidden_states aspen_b200_dnn_set_embedding
+aspen_b200_rpool_add_nasm_tokens aspen_b200_matmul_noalloc""".split()
 
 
 def lib():
@@ -66,7 +67,7 @@ def lib():
         "print_dnn_info": (None, [vp, i]), "print_nasm_info": (None, [vp, i, i]), "print_rpool_info": (None, [vp]),
         "aspen_b200_last_error": (cp, []), "aspen_b200_group_status": (i, [vp]),
         "aspen_b200_set_tile_profile": (None, [i]), "aspen_b200_set_tile_quanta": (None, [u, u, u]),
-        "aspen_b200_set_precision": (None, [i]), "aspen_b200_set_device": (i, [i]),
+        "aspen_b200_set_precision": (None, [i]), "aspen_b200_set_hidden_states": (None, [i]), "aspen_b200_set_device": (i, [i]),
         "aspen_b200_dnn_num_layers": (u, [vp]), "aspen_b200_dnn_layer_params": (None, [vp, u, vp]),
         "aspen_b200_dnn_layer_type": (i, [vp, u]),
         "aspen_b200_nasm_num_ldata": (u, [vp]), "aspen_b200_nasm_num_ninst": (u, [vp]),
@@ -78,6 +79,7 @@ def lib():
         "aspen_b200_group_profile": (i, [vp, vp, C.POINTER(u)]),
         "aspen_b200_generate_nasm": (vp, [vp, u, u, C.POINTER(u)]),
         "aspen_b200_matmul_noalloc": (i, [vp, vp, vp, vp, u, u, u, i, vp]),
+        "aspen_b200_dnn_set_embedding": (i, [vp, vp, u, vp, u]), "aspen_b200_rpool_add_nasm_tokens": (None, [vp, vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -111,6 +113,14 @@ class Dnn:
 
     def layer_type(self, idx: int) -> int:
         return lib().aspen_b200_dnn_layer_type(self.h, idx)
+
+    def set_embedding(self, token_table: np.ndarray, position_table: np.ndarray | None = None) -> None:
+        tok = np.ascontiguousarray(token_table, dtype=np.float32)
+        pos = None if position_table is None else np.ascontiguousarray(position_table, dtype=np.float32)
+        rc = lib().aspen_b200_dnn_set_embedding(self.h, tok.ctypes.data, tok.shape[0], pos.ctypes.data if pos is not None else None,
+                                                pos.shape[0] if pos is not None else 0)
+        if rc != 0:
+            raise RuntimeError("aspen_b200_dnn_set_embedding failed: " + last_error())
 
     def close(self):
         if self.h:
@@ -219,6 +229,11 @@ class Rpool:
         else:
             x = np.ascontiguousarray(x, dtype=np.float32)
             lib().rpool_add_nasm_raw_input(self.h, nasm.h, x.ctypes.data)
+
+    def add_tokens(self, nasm: Nasm, ids: np.ndarray) -> None:
+        """aspen_b200_rpool_add_nasm_tokens: ids [batch][seq] int32, embedded on the device."""
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        lib().aspen_b200_rpool_add_nasm_tokens(self.h, nasm.h, ids.ctypes.data)
 
     def reset(self, nasm: Nasm) -> None:
         lib().rpool_reset_queue(self.h)

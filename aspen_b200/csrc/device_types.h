@@ -36,6 +36,7 @@ struct LayerDev {
     unsigned res_ld_in, res_ld_out;
     int res_act;
     unsigned res_round;
+    unsigned res_elide;       // the layer's own (pre-add) output has no other reader and is not written
 };
 
 struct TileDev {

@@ -33,6 +33,18 @@ extern "C" int aspen_b200_set_device(int device) {
     return cudaSetDevice(device) == cudaSuccess ? 0 : -1;
 }
 
+// Whether every layer's output stays readable after a run (the default), or outputs that only feed a residual add
+// fused into their producer are left unwritten (1 = keep all, 0 = drop those).  Read when a graph's device image is built.
+static thread_local int g_keep_hidden = -1;
+
+extern "C" void aspen_b200_set_hidden_states(int keep) { g_keep_hidden = keep ? 1 : 0; }
+
+static bool keep_hidden_states() {
+    if (g_keep_hidden >= 0) return g_keep_hidden != 0;
+    const char *v = getenv("ASPEN_B200_HIDDEN_STATES");
+    return !(v && *v && atoi(v) == 0);
+}
+
 int engine_current_device() {
     if (g_device >= 0) return g_device;
     if (const char *v = getenv("ASPEN_B200_DEVICE")) {     // for callers that cannot call aspen_b200_set_device
@@ -55,6 +67,7 @@ struct DeviceDnn {
     std::vector<float *> weight_rows;   // tensor-core path, input convolutions with <= 4 channels: k = (kh, [kw][4] padded to 32)
     std::vector<unsigned> ic_pad;     // conv on the network input with IC % 4 != 0: channels padded to this many (0: not padded)
     bool have[2] = {false, false};
+    float *emb_token = nullptr, *emb_position = nullptr;   // embedding tables, uploaded on first use
 };
 
 static float round_to_tf32(float x) {
@@ -149,6 +162,8 @@ void engine_release_dnn(aspen_dnn_t *dnn) {
         for (float *ptr : dd->bias) cudaFree(ptr);
         for (float *ptr : dd->weight_rows) cudaFree(ptr);
         for (float *ptr : dd->anchors) cudaFree(ptr);
+        cudaFree(dd->emb_token);
+        cudaFree(dd->emb_position);
         cudaSetDevice(prev);
         delete dd;
         dd = nullptr;
@@ -201,6 +216,7 @@ struct DeviceNasm {
     // scheduler kernel holds every SM's shared memory); the scatter of a strided input and the gather of the last
     // layer's result are kernels on the compute stream, ordered around the graph's own run.
     float *in_stage = nullptr;          // packed input as uploaded, scattered into layer 0 just before the run
+    int *ids_stage = nullptr;           // token ids as uploaded, gathered into layer 0 just before the run
     float *res_packed = nullptr;        // last layer gathered right after each run
     cudaEvent_t in_consumed = nullptr;  // compute stream: in_stage has been scattered
     cudaEvent_t res_ready = nullptr;    // compute stream: the run (and the gather) are complete
@@ -331,9 +347,9 @@ static int ensure_xfer(Engine *e, size_t bytes) {
     return 0;
 }
 
-// packed [W][H] <-> strided [W][ld] activation matrix.  Launched with 64-thread blocks: a block that small still
-// fits the registers the persistent scheduler kernel leaves free on an SM (it takes 11 warps x 168), so these
-// run next to a graph that is being computed instead of waiting for it.
+// packed [W][H] <-> strided [W][ld] activation matrix.  Small blocks; while a scheduler kernel is resident they wait
+// for it (it takes all but a sliver of every SM's registers and shared memory), which stream order asks for anyway
+// wherever they sit on the compute stream.
 constexpr unsigned XFER_THREADS = 64;
 // layer-0 matrix [pixel][ld] (already rounded) -> interior of the zero-padded [sample][PH][PW][4] copy
 __global__ void fill_padded_input(float *dst, const float *src, unsigned ld, unsigned IC, unsigned IH, unsigned IW, unsigned PH, unsigned PW,
@@ -348,6 +364,26 @@ __global__ void fill_padded_input(float *dst, const float *src, unsigned ld, uns
         if (IC > 2) v.z = p[2];
         if (IC > 3) v.w = p[3];
         reinterpret_cast<float4 *>(dst)[(b * PH + ih + pad) * PW + iw + pad] = v;
+    }
+}
+// Token ids -> layer-0 hidden states: column t (= b * seq + s) is the id's row of the token table plus row s of the
+// position table.  One 16-byte piece per thread and step; consecutive threads take consecutive pieces of a row, so
+// reads of a table row and writes of a column are 128-bit and coalesced.  Ids outside the table are clamped.
+__global__ void embedding_gather(float *dst, unsigned ld, const int *ids, const float *tok, const float *pos, unsigned M, unsigned seq,
+                                 unsigned vocab, size_t n_tokens, int round) {
+    const unsigned m4 = M >> 2;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n_tokens * m4; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / m4;
+        const unsigned j = (unsigned)(i - t * m4) * 4u;
+        int id = ids[t];
+        id = id < 0 ? 0 : (id >= (int)vocab ? (int)vocab - 1 : id);
+        float4 v = __ldg(reinterpret_cast<const float4 *>(tok + (size_t)id * M + j));
+        if (pos) {
+            const float4 p = __ldg(reinterpret_cast<const float4 *>(pos + (size_t)(t % seq) * M + j));
+            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        if (round) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
+        *reinterpret_cast<float4 *>(dst + t * ld + j) = v;
     }
 }
 __global__ void unpack_columns(float *dst, const float *src, unsigned H, unsigned ld, size_t n, int round) {
@@ -415,7 +451,7 @@ static void free_device_nasm(DeviceNasm *dn) {
     cudaFree(dn->dep_init); cudaFree(dn->layer_done); cudaFree(dn->layer_tiles); cudaFree(dn->init_ready);
     cudaFree(dn->layers_completed); cudaFree(dn->layer_done_init); cudaFree(dn->wmaps);
     if (dn->completed_h) cudaFreeHost(dn->completed_h);
-    cudaFree(dn->in_stage); cudaFree(dn->res_packed); cudaFree(dn->padded_in);
+    cudaFree(dn->in_stage); cudaFree(dn->ids_stage); cudaFree(dn->res_packed); cudaFree(dn->padded_in);
     if (dn->in_consumed) cudaEventDestroy(dn->in_consumed);
     if (dn->res_ready) cudaEventDestroy(dn->res_ready);
     delete dn;
@@ -630,6 +666,13 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
             L.res_in = layers[lo].out; L.res_ld_in = layers[lo].ldc;
             L.res_out = layers[i].out; L.res_ld_out = layers[i].ldc;
             L.res_act = layers[i].act; L.res_round = layers[i].round_out;
+            // The producer's own (pre-add) output: the reference frees it as soon as the residual layer has read it
+            // (src/dse.c:84-92).  When nothing else reads it and the caller has not asked for every hidden state,
+            // it is not written at all.
+            bool only_reader = true;
+            for (unsigned j = 1; j < nasm->num_ldata; j++)
+                if (j != i && (nasm->ldata[j].parent_ldata_idx_arr[PARENT_0] == hi || nasm->ldata[j].parent_ldata_idx_arr[PARENT_1] == hi)) only_reader = false;
+            L.res_elide = (!keep_hidden_states() && only_reader && hi != nasm->num_ldata - 1) ? 1u : 0u;
             fused_other[hi] = lo;
             written_by_parents[i] = 1;
         }
@@ -802,6 +845,47 @@ int engine_set_input(nasm_t *nasm, const void *input_host) {
         e->launches++;
         CUDA_TRY(cudaGetLastError());
     }
+    return 0;
+}
+
+int engine_set_tokens(nasm_t *nasm, const int *ids_host) {
+    DeviceNasm *dn = nasm->dev;
+    if (!dn || !ids_host) return -1;
+    Engine *e = dn->e;
+    aspen_dnn_t *dnn = nasm->dnn;
+    CUDA_TRY(cudaSetDevice(e->device));
+    const nasm_ldata_t &l0 = nasm->ldata[0];
+    const unsigned M = l0.out_mat_dims[OUT_H];
+    const size_t n_tokens = l0.out_mat_dims[OUT_W];
+    if (dnn->emb_token.empty() || dnn->emb_width != M || M % 4 != 0 || l0.out_mat_stride % 4 != 0) {
+        ASPEN_ERR("token input: the dnn has no embedding table of width %u (aspen_b200_dnn_set_embedding), or the width is not a multiple of 4\n", M);
+        return -1;
+    }
+    if (!dnn->emb_position.empty() && nasm->tr_seq_len > dnn->emb_max_pos) { ASPEN_ERR("token input: sequence length %u exceeds the position table (%u rows)\n", nasm->tr_seq_len, dnn->emb_max_pos); return -1; }
+    DeviceDnn *dd = dn->dd;
+    if (!dd->emb_token) {
+        CUDA_TRY(cudaMalloc(&dd->emb_token, dnn->emb_token.size() * sizeof(float)));
+        CUDA_TRY(cudaMemcpy(dd->emb_token, dnn->emb_token.data(), dnn->emb_token.size() * sizeof(float), cudaMemcpyHostToDevice));
+        if (!dnn->emb_position.empty()) {
+            CUDA_TRY(cudaMalloc(&dd->emb_position, dnn->emb_position.size() * sizeof(float)));
+            CUDA_TRY(cudaMemcpy(dd->emb_position, dnn->emb_position.data(), dnn->emb_position.size() * sizeof(float), cudaMemcpyHostToDevice));
+        }
+    }
+    if (!dn->ids_stage) CUDA_TRY(cudaMalloc(&dn->ids_stage, n_tokens * sizeof(int)));
+    cudaStream_t io = io_stream(e, nasm);
+    dn->res_valid = false;
+    // ids by DMA on the transfer stream (after the previous gather has read the staging copy), gather on the compute stream
+    CUDA_TRY(cudaStreamWaitEvent(io, dn->in_consumed, 0));
+    CUDA_TRY(cudaMemcpyAsync(dn->ids_stage, ids_host, n_tokens * sizeof(int), cudaMemcpyHostToDevice, io));
+    CUDA_TRY(cudaStreamSynchronize(io));     // the caller may reuse its buffer as soon as we return
+    float *dst = (float *)((char *)dn->arena + dn->ldata_off[0]);
+    const size_t work = n_tokens * (M / 4);
+    embedding_gather<<<(unsigned)std::min<size_t>((work + 255) / 256, 4096), 256, 0, e->stream>>>(
+        dst, l0.out_mat_stride, dn->ids_stage, dd->emb_token, dd->emb_position, M, nasm->tr_seq_len ? nasm->tr_seq_len : 1u, dnn->emb_vocab, n_tokens,
+        dn->round_input ? 1 : 0);
+    e->launches++;
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaEventRecord(dn->in_consumed, e->stream));
     return 0;
 }
 

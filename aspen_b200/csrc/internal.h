@@ -45,6 +45,10 @@ struct aspen_dnn_t {
     unsigned int num_layers = 0;
     std::atomic<unsigned int> ref_nasms{0};
     DeviceDnn *dev[16] = {};   // per-CUDA-device weight copies, created on first use
+    // Embedding tables of a transformer whose cfg starts at the hidden states (aspen_b200_dnn_set_embedding):
+    // token_table [vocab][M], position_table [max_pos][M] (may be empty).
+    std::vector<float> emb_token, emb_position;
+    unsigned int emb_vocab = 0, emb_max_pos = 0, emb_width = 0;
 };
 
 struct ninst_t {
@@ -171,6 +175,7 @@ void engine_destroy(Engine *e);
 int engine_attach_nasm(Engine *e, nasm_t *nasm, const void *input_host);   // upload image + input
 void engine_detach_nasm(nasm_t *nasm);
 int engine_set_input(nasm_t *nasm, const void *input_host);
+int engine_set_tokens(nasm_t *nasm, const int *token_ids_host);   // layer 0 = embedding rows of the ids, gathered on the device
 int engine_rearm(Engine *e, nasm_t *nasm);
 int engine_run(Engine *e, const std::vector<nasm_t *> &nasms);
 int engine_stop(Engine *e);

@@ -57,6 +57,35 @@ extern "C" void rpool_add_nasm_raw_input(rpool_t *rpool, nasm_t *nasm, void *inp
     }
 }
 
+// Token-id input of a transformer (no counterpart in the reference, whose cfgs start at the hidden states).
+extern "C" int aspen_b200_dnn_set_embedding(aspen_dnn_t *dnn, const float *token_table, unsigned int vocab, const float *position_table,
+                                            unsigned int max_pos) {
+    if (!dnn || !token_table || vocab == 0) { ASPEN_ERR("ERROR: aspen_b200_dnn_set_embedding: NULL dnn / table or empty vocabulary.\n"); return -1; }
+    const unsigned int width = dnn->layers.empty() ? 0 : dnn->layers[0].params[MAT_M];
+    if (width == 0) { ASPEN_ERR("ERROR: aspen_b200_dnn_set_embedding: the first layer of dnn \"%s\" has no hidden width (M).\n", dnn->name); return -1; }
+    for (DeviceDnn *dd : dnn->dev)
+        if (dd) { ASPEN_ERR("ERROR: aspen_b200_dnn_set_embedding: set the tables before the dnn's first graph is uploaded.\n"); return -1; }
+    dnn->emb_token.assign(token_table, token_table + (size_t)vocab * width);
+    dnn->emb_position.clear();
+    if (position_table && max_pos) dnn->emb_position.assign(position_table, position_table + (size_t)max_pos * width);
+    dnn->emb_vocab = vocab; dnn->emb_max_pos = position_table ? max_pos : 0; dnn->emb_width = width;
+    return 0;
+}
+
+extern "C" void aspen_b200_rpool_add_nasm_tokens(rpool_t *rpool, nasm_t *nasm, const int *token_ids) {
+    if (!rpool || !nasm || !token_ids) { ASPEN_ERR("ERROR: aspen_b200_rpool_add_nasm_tokens: NULL argument.\n"); return; }
+    if (!rpool->engine) { ASPEN_ERR("ERROR: aspen_b200_rpool_add_nasm_tokens: attach the rpool to a dse group first (the gather runs on its device).\n"); return; }
+    // the graph joins the pool exactly as with a raw input (image built on first use); layer 0 is then filled from the ids
+    if (!nasm->dev || nasm->rpool != rpool) {
+        rpool_add_nasm_raw_input(rpool, nasm, nullptr);
+        if (!nasm->dev) return;
+    } else {
+        nasm->completed.store(0);
+        if (engine_rearm(rpool->engine, nasm) != 0) return;
+    }
+    if (engine_set_tokens(nasm, token_ids) != 0) ASPEN_ERR("ERROR: aspen_b200_rpool_add_nasm_tokens: device gather failed.\n");
+}
+
 extern "C" void rpool_add_nasm(rpool_t *rpool, nasm_t *nasm, char *input_filename) {
     if (!rpool || !nasm) { ASPEN_ERR("ERROR: rpool_add_nasm: NULL argument.\n"); return; }
     const aspen_layer_t &first = nasm->dnn->layers[0];

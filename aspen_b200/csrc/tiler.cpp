@@ -122,8 +122,14 @@ void tiler_init_ldata(nasm_t *nasm, nasm_ldata_t *ld, aspen_layer_t *layer) {
     if (whole_column) t[OUT_H] = (unsigned int)round_up(dim[OUT_H], q.h_min);
     if (type == SOFTMAX_LAYER) t[OUT_W] = 1;
     if (type == FC_LAYER && dim[OUT_W] < unit_w) unit_w = dim[OUT_W];
-    if (layer->params[NUM_HEAD] > 0) {
-        hidden_per_head = layer->params[NUM_HIDDEN] / layer->params[NUM_HEAD];
+    // The reference cuts every layer that carries a head count into tiles of at most one head's rows and lets their
+    // width shrink to 8 columns.  With tensor-core quanta the query / key / value projections (plain matmuls whose
+    // consumers address heads by offset) keep whole MMA blocks instead: a 64-row tile stages half the FLOP per byte
+    // of a 256-row one.
+    const bool ref_quanta = q.h_min == NINST_H_MIN && q.w_min == NINST_W_MIN;
+    const bool per_head = layer->params[NUM_HEAD] > 0 && (ref_quanta || type != MATMUL_LAYER);
+    if (layer->params[NUM_HEAD] > 0) hidden_per_head = layer->params[NUM_HIDDEN] / layer->params[NUM_HEAD];
+    if (per_head) {
         unit_w = 8;
         unit_h = hidden_per_head / 4;
     }
@@ -148,7 +154,7 @@ void tiler_init_ldata(nasm_t *nasm, nasm_ldata_t *ld, aspen_layer_t *layer) {
             if (t[OUT_W] <= unit_w && (t[OUT_H] <= unit_h || h_fixed)) break;   // cannot shrink further
         }
     }
-    if (layer->params[NUM_HEAD] > 0 || type == LAYERNORM_LAYER) {
+    if (per_head || type == LAYERNORM_LAYER) {
         // Transformer layers: a tile never straddles heads; layernorm and attention scores take a
         // whole column; the column count is rescaled to keep the tile area and made to divide seq.
         const unsigned int old_h = t[OUT_H];

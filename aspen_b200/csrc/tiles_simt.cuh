@@ -29,6 +29,27 @@ __device__ __forceinline__ float activate(float x, int act) {
     }
 }
 
+// GELU for the tensor-core epilogue, where 128 values per thread go through it.  The library erff / tanhf
+// cost an order of magnitude more there than the contraction's own main loop; these forms are accurate to a
+// few 1e-7 (far inside the TF32 bound) and branch-free.  The fp32 validation mode keeps `activate`.
+//   erf: Abramowitz & Stegun 7.1.26, |error| <= 1.5e-7;  tanh(u) = 1 - 2 / (1 + exp(2u)), u clamped to +-15.
+__device__ __forceinline__ float gelu_erf_fast(float x) {
+    const float z = fabsf(x) * 0.7071067811865475f;
+    const float t = __fdividef(1.f, fmaf(0.3275911f, z, 1.f));
+    float p = fmaf(1.061405429f, t, -1.453152027f);
+    p = fmaf(p, t, 1.421413741f);
+    p = fmaf(p, t, -0.284496736f);
+    p = fmaf(p, t, 0.254829592f);
+    const float erf_abs = 1.f - p * t * __expf(-z * z);
+    return 0.5f * x * (1.f + copysignf(erf_abs, x));
+}
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+    float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    u = fminf(fmaxf(u, -15.f), 15.f);
+    const float th = 1.f - __fdividef(2.f, 1.f + __expf(2.f * u));
+    return 0.5f * x * (1.f + th);
+}
+
 // The tensor cores read only the upper 19 bits of an fp32 operand (TF32), i.e. they truncate.
 // Truncation is biased toward zero and the bias compounds over a deep network, so every layer whose
 // output feeds a tensor-core layer stores values already rounded to nearest TF32; the later
@@ -99,35 +120,74 @@ static __device__ __noinline__ void tile_residual(const LayerDev L, const TileDe
 }
 
 // ref src/tiled_kernels.c:411-501.  Max ignores padded taps (all padded -> -inf); average divides by
-// the full window size, padding counted.
+// the full window size, padding counted.  A thread owns four channels of an output pixel and works on two such
+// items at a time; the window's taps are fetched nine at a time (a whole 3 x 3 window), all loads of both items
+// issued before the first is used (a tap outside the image reads nothing and contributes the neutral element),
+// so the tile is bound by bandwidth instead of one load latency per tap.
 template <bool IS_MAX>
 static __device__ __noinline__ void tile_pool(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
     const unsigned h4 = T.tile_h >> 2, per_col = h4 + (T.tile_h & 3);
     const float inv = 1.f / (float)(L.KH * L.KW);
-    for (unsigned i = tid; i < T.tile_w * per_col; i += nthr) {
-        unsigned n = i / per_col, j = i - n * per_col;
-        size_t col = T.pos_w + n;
-        PixelWin w = pixel_window(L, (unsigned)col);
-        bool vec = j < h4;
-        unsigned m = T.pos_h + (vec ? 4 * j : 4 * h4 + (j - h4));
-        const float init = IS_MAX ? -INFINITY : 0.f;
-        float4 acc = {init, init, init, init};
-        for (int kh = 0; kh < (int)L.KH; kh++)
-            for (int kw = 0; kw < (int)L.KW; kw++) {
-                const float *src = input_pixel(L, w, kh, kw);
-                if (!src) continue;
-                float4 v;
-                if (vec) v = ldcg4(src + m);
-                else { v.x = ldcg1(src + m); v.y = v.z = v.w = 0.f; }
-                if (IS_MAX) { acc.x = acc.x >= v.x ? acc.x : v.x; acc.y = acc.y >= v.y ? acc.y : v.y; acc.z = acc.z >= v.z ? acc.z : v.z; acc.w = acc.w >= v.w ? acc.w : v.w; }
-                else { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+    const float init = IS_MAX ? -INFINITY : 0.f;
+    const unsigned taps = L.KH * L.KW, total = T.tile_w * per_col;
+    constexpr unsigned G = 9, U = 2;
+    for (unsigned i0 = tid; i0 < total; i0 += nthr * U) {
+        PixelWin w[U];
+        unsigned m[U];
+        size_t col[U];
+        bool vec[U], live[U];
+        float4 acc[U];
+        #pragma unroll
+        for (unsigned u = 0; u < U; u++) {
+            const unsigned i = i0 + u * nthr;
+            live[u] = i < total;
+            const unsigned n = live[u] ? i / per_col : 0u, j = live[u] ? i - n * per_col : 0u;
+            col[u] = T.pos_w + n;
+            w[u] = pixel_window(L, (unsigned)col[u]);
+            vec[u] = j < h4;
+            m[u] = T.pos_h + (vec[u] ? 4 * j : 4 * h4 + (j - h4));
+            acc[u] = make_float4(init, init, init, init);
+        }
+        unsigned kh = 0, kw = 0;
+        for (unsigned t0 = 0; t0 < taps; t0 += G) {
+            float4 v[U][G];
+            #pragma unroll
+            for (unsigned g = 0; g < G; g++) {
+                const bool tap_ok = t0 + g < taps;
+                #pragma unroll
+                for (unsigned u = 0; u < U; u++) {
+                    v[u][g] = make_float4(init, init, init, init);
+                    if (tap_ok && live[u]) {
+                        const float *src = input_pixel(L, w[u], (int)kh, (int)kw);
+                        if (src) {
+                            if (vec[u]) v[u][g] = ldcg4(src + m[u]);
+                            else v[u][g].x = ldcg1(src + m[u]);
+                        }
+                    }
+                }
+                if (tap_ok && ++kw == L.KW) { kw = 0; kh++; }
             }
-        if (!IS_MAX) { acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv; }
-        if (vec) {
-            float4 o = {finish(acc.x, L), finish(acc.y, L), finish(acc.z, L), finish(acc.w, L)};
-            *reinterpret_cast<float4 *>(L.out + col * L.ldc + m) = o;
-        } else {
-            L.out[col * L.ldc + m] = finish(acc.x, L);
+            #pragma unroll
+            for (unsigned u = 0; u < U; u++) {
+                #pragma unroll
+                for (unsigned g = 0; g < G; g++) {
+                    const float4 x = v[u][g];
+                    if (IS_MAX) { acc[u].x = acc[u].x >= x.x ? acc[u].x : x.x; acc[u].y = acc[u].y >= x.y ? acc[u].y : x.y; acc[u].z = acc[u].z >= x.z ? acc[u].z : x.z; acc[u].w = acc[u].w >= x.w ? acc[u].w : x.w; }
+                    else { acc[u].x += x.x; acc[u].y += x.y; acc[u].z += x.z; acc[u].w += x.w; }
+                }
+            }
+        }
+        #pragma unroll
+        for (unsigned u = 0; u < U; u++) {
+            if (!live[u]) continue;
+            float4 a = acc[u];
+            if (!IS_MAX) { a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv; }
+            if (vec[u]) {
+                float4 o = {finish(a.x, L), finish(a.y, L), finish(a.z, L), finish(a.w, L)};
+                *reinterpret_cast<float4 *>(L.out + col[u] * L.ldc + m[u]) = o;
+            } else {
+                L.out[col[u] * L.ldc + m[u]] = finish(a.x, L);
+            }
         }
     }
 }
@@ -142,14 +202,49 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // ref src/tiled_kernels.c:743-783: one pass mean / E[x^2], eps 1e-6, gain and shift.  One warp per column.
+// A column of up to 1024 features is read ONCE: each lane keeps its up to eight 16-byte pieces in registers (all
+// loads issued before the first use), the warp reduces sum and sum of squares, and the normalised values are
+// written from the registers.  Longer or unaligned columns take the two-pass loop.
 static __device__ __noinline__ void tile_layernorm(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
     const unsigned warp = tid >> 5, lane = tid & 31, nwarp = nthr >> 5;
     const unsigned M = T.tile_h;
     const float *gain = L.weight + T.pos_h;
     const float *shift = L.bias ? L.bias + T.pos_h : nullptr;
+    const bool in_regs = M <= 1024u && (M & 3u) == 0u && ((L.ld0 | L.ldc | T.pos_h) & 3u) == 0u;
     for (unsigned n = warp; n < T.tile_w; n += nwarp) {
         const float *x = L.in0 + (size_t)(T.pos_w + n) * L.ld0 + T.pos_h;
         float *y = L.out + (size_t)(T.pos_w + n) * L.ldc + T.pos_h;
+        if (in_regs) {
+            float4 v[8];
+            #pragma unroll
+            for (unsigned q = 0; q < 8; q++) {
+                const unsigned m = lane * 4u + q * 128u;
+                v[q] = m < M ? ldcg4(x + m) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            float s = 0.f, ss = 0.f;
+            #pragma unroll
+            for (unsigned q = 0; q < 8; q++) {
+                s += v[q].x + v[q].y + v[q].z + v[q].w;
+                ss += v[q].x * v[q].x + v[q].y * v[q].y + v[q].z * v[q].z + v[q].w * v[q].w;
+            }
+            s = warp_sum(s);
+            ss = warp_sum(ss);
+            const float mean = s / (float)M;
+            const float var = ss / (float)M - mean * mean;
+            const float inv = 1.f / sqrtf(var + 1e-6f);
+            #pragma unroll
+            for (unsigned q = 0; q < 8; q++) {
+                const unsigned m = lane * 4u + q * 128u;
+                if (m < M) {
+                    const float4 g = *reinterpret_cast<const float4 *>(gain + m);
+                    float4 o = {(v[q].x - mean) * inv * g.x, (v[q].y - mean) * inv * g.y, (v[q].z - mean) * inv * g.z, (v[q].w - mean) * inv * g.w};
+                    if (shift) { const float4 b = *reinterpret_cast<const float4 *>(shift + m); o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w; }
+                    o.x = store_round(o.x, L); o.y = store_round(o.y, L); o.z = store_round(o.z, L); o.w = store_round(o.w, L);
+                    *reinterpret_cast<float4 *>(y + m) = o;
+                }
+            }
+            continue;
+        }
         float s = 0.f, ss = 0.f;
         const unsigned M4 = M & ~3u;
         for (unsigned m = lane * 4; m < M4; m += 128) {

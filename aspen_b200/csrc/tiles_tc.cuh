@@ -214,10 +214,11 @@ __device__ __forceinline__ void store_block_coalesced(float *stage /*warp's 4 KB
 
 // Same block store, plus the fused residual layer (ref src/tiled_kernels.c:503-541 computes it as a layer
 // of its own): out2 = act(value + in2) for the same 32 x 32 block, read and written in the coalesced
-// layout.  The eight loads of in2 are issued before the first store so they overlap.
+// layout.  The eight loads of in2 are issued before the first store so they overlap.  `elide_own`: the
+// pre-add value itself has no reader and is not stored.
 __device__ __forceinline__ void store_block_residual(float *stage, const float *v, float *out_block, size_t ldc, unsigned n_valid,
                                                      unsigned m_valid, const float *in2_block, size_t ld_in2, float *out2_block,
-                                                     size_t ld_out2, int act2, bool round2) {
+                                                     size_t ld_out2, int act2, bool round2, bool elide_own) {
     const unsigned lane = threadIdx.x & 31u;
     float4 *st = reinterpret_cast<float4 *>(stage);
     #pragma unroll
@@ -249,11 +250,13 @@ __device__ __forceinline__ void store_block_residual(float *stage, const float *
         if (round2) o = make_float4(tf32_round(o.x), tf32_round(o.y), tf32_round(o.z), tf32_round(o.w));
         if (n < n_valid) {
             float *dst = out_block + (size_t)n * ldc + m, *dst2 = out2_block + (size_t)n * ld_out2 + m;
-            if (full) { *reinterpret_cast<float4 *>(dst) = val; *reinterpret_cast<float4 *>(dst2) = o; }
-            else {
-                if (m < m_valid) { dst[0] = val.x; dst2[0] = o.x; }
-                if (m + 1u < m_valid) { dst[1] = val.y; dst2[1] = o.y; }
-                if (m + 2u < m_valid) { dst[2] = val.z; dst2[2] = o.z; }
+            if (full) {
+                if (!elide_own) *reinterpret_cast<float4 *>(dst) = val;
+                *reinterpret_cast<float4 *>(dst2) = o;
+            } else {
+                if (m < m_valid) { if (!elide_own) dst[0] = val.x; dst2[0] = o.x; }
+                if (m + 1u < m_valid) { if (!elide_own) dst[1] = val.y; dst2[1] = o.y; }
+                if (m + 2u < m_valid) { if (!elide_own) dst[2] = val.z; dst2[2] = o.z; }
             }
         }
     }
@@ -602,6 +605,12 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                             if (act == RELU) {
                                 #pragma unroll
                                 for (unsigned j = 0; j < 32; j++) v[j] = fmaxf(v[j], 0.f);
+                            } else if (act == GELU) {
+                                #pragma unroll
+                                for (unsigned j = 0; j < 32; j++) v[j] = gelu_erf_fast(v[j]);
+                            } else if (act == GELU_ACCURATE) {
+                                #pragma unroll
+                                for (unsigned j = 0; j < 32; j++) v[j] = gelu_tanh_fast(v[j]);
                             } else if (act != NO_ACTIVATION && act != LINEAR) {
                                 #pragma unroll
                                 for (unsigned j = 0; j < 32; j++) v[j] = activate(v[j], act);
@@ -615,7 +624,7 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                             if (L.res_out) {
                                 const size_t col0 = T.pos_w + n0 + lane_base, m0 = T.pos_h + ms + c * 32u;
                                 store_block_residual(epi, v, oblk + c * 32u, L.ldc, n_valid, valid, L.res_in + col0 * L.res_ld_in + m0, L.res_ld_in,
-                                                     L.res_out + col0 * L.res_ld_out + m0, L.res_ld_out, L.res_act, L.res_round != 0);
+                                                     L.res_out + col0 * L.res_ld_out + m0, L.res_ld_out, L.res_act, L.res_round != 0, L.res_elide != 0);
                             } else store_block_coalesced(epi, v, oblk + c * 32u, L.ldc, n_valid, valid);
                         }
                     }

@@ -10,6 +10,12 @@ its own GPU -- independent shards, no collective on the data path, weak scaling 
 prints one JSON line with the whole-job inferences/s, timed on the device (CUDA events on the
 engine's stream) as the maximum over ranks.
 
+The device-timed region is repeated `--blocks` times (each exactly `--steps` passes) and the median
+block is reported.  Beside the headline the line carries: `e2e` (host input -> H2D -> run -> D2H through
+the public calls), `bert_base` (BERT-base S128 batch 32, the other half of the metric), and for N > 1
+`strong` (the global batch of 32 split 32/N per GPU, results gathered on rank 0 in batch order) and
+`by_model` (ResNet-50 batch 16 on one half of the GPUs, VGG-16 batch 16 on the other half).
+
 `--impl reference` times the unmodified reference's pthread/AVX2 path (oracle/_ref, built from the
 reference sources) on the host cores for the same workload.
 """
@@ -33,13 +39,14 @@ WORKLOADS = {
     # name: (cfg builder, batch per GPU, seq, weight scheme, weight seed, input seed, per-sample input shape)
     "resnet50": ("resnet50", 32, 0, "he", 1, 0),
     "bert_base": ("bert_base", 32, 128, "n002", 3, 3),
+    "vgg16": ("vgg16", 16, 0, "he", 2, 2),
 }
 # DRAM bytes per scheduler launch, from the ncu capture summarised in profiles/ (batch-4 case scaled by 8).
 TRAFFIC_BYTES = {"resnet50": 2.3e9}
 # Tiling of the nasm per workload: (row quantum, column quantum, min_ninst_per_ldata).  Tensor-core shaped
 # quanta; the values a graph computes do not depend on them.  Each is the best of a measured sweep
 # (quanta 64-256, min_ninst 100-592).
-TILING = {"resnet50": (128, 128, 180), "bert_base": (256, 128, 296)}
+TILING = {"resnet50": (128, 128, 180), "bert_base": (256, 128, 296), "vgg16": (128, 128, 180)}
 
 
 def log(*a):
@@ -77,6 +84,16 @@ class ClockSampler(threading.Thread):
                 self.rows.append([c.strip() for c in line.split(",")])
         except Exception:
             pass
+
+    def wait_first(self, timeout: float):
+        """Blocks until the first sample has arrived (nvidia-smi needs a second or more to start, longer when eight
+        ranks start one each), so that the timed region that follows is covered."""
+        t0 = time.time()
+        while not self.rows and time.time() - t0 < timeout:
+            time.sleep(0.05)
+        if not self.rows:
+            log(f"clock sampler: no nvidia-smi sample for GPU {self.index} after {timeout:.0f} s")
+        self.rows.clear()       # samples taken before the timed region do not count
 
     def stop(self):
         if self.proc:
@@ -195,14 +212,147 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+class Net:
+    """One network on this rank's GPU, driven through the public API: dnn + `graphs` tile graphs (nasms) of the same
+    batch in one rpool, one dse group, a pinned host input."""
+
+    def __init__(self, workload: str, batch: int, workdir: str, graphs: int = 2, min_ninst: int | None = None, group=None, rpool=None):
+        import torch
+        from aspen_b200 import api
+        self.api, self.L = api, api.lib()
+        self.workload, self.batch = workload, batch
+        builder, _, self.seq, scheme, wseed, iseed = WORKLOADS[workload]
+        self.cfg, self.wfile = prepare_files(workload, workdir)
+        q_h, q_w, mn = TILING[workload]
+        self.tiling = (q_h, q_w, min_ninst or mn)
+        self.L.aspen_b200_set_tile_quanta(q_h, q_w, 100000000)
+        self.dnn = api.Dnn(self.cfg, self.wfile)
+        self.nasms = [api.Nasm(self.dnn, batch, self.seq, self.tiling[2]) for _ in range(graphs)]
+        self.L.aspen_b200_set_tile_profile(0)
+        self.own_group = group is None
+        self.rpool = rpool or api.Rpool()
+        self.group = group or api.DseGroup(0, 0)
+        if self.own_group:
+            self.group.set_rpool(self.rpool)
+        i0 = self.nasms[0].ldata_info(0)
+        shape = (i0["W"], i0["H"])
+        self.x_pinned = torch.empty(shape, dtype=torch.float32).pin_memory()
+        self.x_pinned.copy_(torch.from_numpy(np.random.default_rng(iseed).standard_normal(shape, dtype=np.float32)))
+        self.x = self.x_pinned.numpy()
+        self.order = [api.BATCH, api.OUT_C, api.OUT_H, api.OUT_W] if self.seq == 0 else [api.BATCH, api.MAT_N, api.MAT_M]
+        self.flops = self.nasms[0].total_flops
+        self.arena_bytes = sum(self.nasms[0].ldata_info(i)["mem_size"] for i in range(self.nasms[0].num_ldata))
+        self.out = None
+
+    def warm(self):
+        """Device images built, first touch done, one graph armed for the device-timed runs."""
+        for n_ in self.nasms:
+            self.rpool.add(n_, self.x); self.group.run(); self.group.wait(n_); self.group.stop(); self.out = n_.result(self.order)
+        self.rpool.add(self.nasms[0], self.x)
+
+    def time_blocks(self, warmup: int, steps: int, blocks: int):
+        """`blocks` device-timed regions (CUDA events on the engine's stream) of exactly `steps` back-to-back passes of one graph."""
+        ms, launches = [], 0
+        for b in range(blocks):
+            t, launches = self.group.time_runs(warmup if b == 0 else 1, steps)
+            ms.append(t)
+        return ms, launches
+
+    def e2e_serial(self, steps: int) -> float:
+        nasm = self.nasms[0]
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            self.rpool.add(nasm, self.x)      # rpool_add_nasm_raw_input: host -> device copy of this step's input
+            self.group.run()
+            self.group.wait(nasm)
+            self.group.stop()
+            self.out = nasm.result(self.order)  # dse_get_nasm_result: device -> host read of the step's result
+        return (time.perf_counter() - t0) * 1e3
+
+    def e2e_overlapped(self, steps: int) -> float:
+        """Same calls, two graphs of the network in flight (the serving loop of a user who double-buffers): while the
+        scheduler kernel works on one graph, the next step's input uploads and the previous step's result downloads on
+        the library's transfer stream.  Every timed iteration still contains one host -> device input copy, one
+        completed graph and one device -> host result read."""
+        pair, cur = self.nasms[:2], 0
+        t0 = time.perf_counter()
+        self.rpool.add(pair[cur], self.x); self.group.run()      # step 1 starts inside the timed region
+        out = None
+        for _ in range(steps - 1):
+            nxt = cur ^ 1
+            self.rpool.add(pair[nxt], self.x)   # upload of the next step's input, under the current graph's kernel
+            self.group.wait(pair[cur])
+            self.group.stop()
+            self.group.run()                    # next graph starts
+            out = pair[cur].result(self.order)  # result of the finished graph, under the next graph's kernel
+            cur = nxt
+        self.group.wait(pair[cur]); self.group.stop(); out2 = pair[cur].result(self.order)
+        ms = (time.perf_counter() - t0) * 1e3   # exactly `steps` uploads, runs and downloads
+        assert np.isfinite(out2).all() and (out is None or np.array_equal(out, out2))
+        self.out = out2
+        return ms
+
+    def close(self):
+        if self.own_group:
+            self.group.close()
+        for n_ in reversed(self.nasms):
+            n_.close()
+        if self.own_group:
+            self.rpool.close()
+        self.dnn.close()
+
+
+def measure_matmul_peaks():
+    """Dense TF32 tensor peak of this GPU, measured the way MEASURED_PEAKS.json measures bf16: torch.matmul 8192^3
+    with TF32 enabled, best of 10 (burst) and back to back for about 2 s (sustained)."""
+    import torch
+    torch.backends.cuda.matmul.allow_tf32 = True
+    n = 8192
+    a = torch.randn(n, n, device="cuda"); b = torch.randn(n, n, device="cuda")
+    for _ in range(3):
+        a @ b
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); a @ b; e1.record(); torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0, k = time.time(), 0
+    e0.record()
+    while time.time() - t0 < 2.0:
+        for _ in range(20):
+            a @ b
+        k += 20
+        torch.cuda.synchronize()
+    e1.record(); torch.cuda.synchronize()
+    flop = 2.0 * n ** 3
+    del a, b
+    torch.cuda.empty_cache()
+    return {"tf32_tflops": flop / best / 1e9, "tf32_tflops_sustained": flop * k / e0.elapsed_time(e1) / 1e9}
+
+
+def gather_rows(local: np.ndarray, world: int):
+    """Results of all ranks on rank 0, in rank (= batch) order.  NCCL moves a few KB of logits after the timed region;
+    the data path itself has no collective."""
+    import torch
+    import torch.distributed as dist
+    t = torch.from_numpy(np.ascontiguousarray(local)).cuda()
+    parts = [torch.empty_like(t) for _ in range(world)] if dist.get_rank() == 0 else None
+    dist.gather(t, parts, dst=0)
+    return np.concatenate([p.cpu().numpy() for p in parts]) if parts else None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--blocks", type=int, default=5, help="repetitions of the device-timed region; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="headline only: no BERT-base, strong-scaling or by-model legs")
     ap.add_argument("--dry-run", action="store_true", help="no GPU: exercise launch, barrier and aggregation with fake timings")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.dry_run else args.warmup
@@ -214,139 +364,191 @@ def main():
     use_cuda = not args.dry_run
     init_dist(world, local_rank, use_cuda)
     workload = args.workload
-    builder, batch, seq, scheme, wseed, iseed = WORKLOADS[workload]
+    batch = WORKLOADS[workload][1]
 
     if args.dry_run:
         barrier(world, False)
         my_ms = 10.0 * args.steps * (1.0 + 0.1 * rank)
         max_ms = reduce_max(my_ms, world, False)
+        # strong split of the global batch (32 samples -> 32 / world per rank) and the by-model split, as the GPU path shards them
+        shard = strong_shard(batch, rank, world)
+        model = by_model_assignment(rank, world)
+        parts = gather_objects((rank, shard, model), world)
         barrier(world, False)
         if rank == 0:
             print(json.dumps({"metric": "inferences_per_sec", "value": job_value(batch, args.steps, world, max_ms), "unit": "inf/s",
                               "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": max_ms / args.steps,
-                              "scaling": "weak", "data": "dry-run", "higher_is_better": True}), flush=True)
+                              "scaling": "weak", "data": "dry-run", "higher_is_better": True,
+                              "strong": {"shards": [p[1] for p in parts]}, "by_model": {"assignment": [p[2] for p in parts]}}), flush=True)
         return
 
-    import torch
     from aspen_b200 import api
     L = api.lib()
     if L.aspen_b200_set_device(local_rank) != 0:
         raise SystemExit("no CUDA device for this rank: " + api.last_error())
     wd = tempfile.mkdtemp(prefix=f"aspen_bench_r{rank}_")
-    cfg, wfile = prepare_files(workload, wd)
 
-    q_h, q_w, min_ninst = TILING[workload]
-    L.aspen_b200_set_tile_quanta(q_h, q_w, 100000000)
-    dnn = api.Dnn(cfg, wfile)
-    nasm = api.Nasm(dnn, batch, seq, min_ninst)
-    L.aspen_b200_set_tile_profile(0)
-    rpool = api.Rpool()
-    group = api.DseGroup(0, 0)
-    group.set_rpool(rpool)
-    i0 = nasm.ldata_info(0)
-    in_shape = (i0["W"], i0["H"])
-    x_pinned = torch.empty(in_shape, dtype=torch.float32).pin_memory()
-    x_pinned.copy_(torch.from_numpy(np.random.default_rng(iseed).standard_normal(in_shape, dtype=np.float32)))
-    x = x_pinned.numpy()
-    rpool.add(nasm, x)
-    arena_bytes = sum(nasm.ldata_info(i)["mem_size"] for i in range(nasm.num_ldata))
-    flops = nasm.total_flops
-
-    # ---- device-timed runs (inputs resident in HBM) ----
-    group.time_runs(1, 1)                                   # first touch outside the timed region
-    barrier(world, True)
     sampler = ClockSampler(local_rank)
     sampler.start()
-    time.sleep(0.3)
-    ms, launches = group.time_runs(args.warmup, args.steps)
-    clocks = sampler.stop()
-    max_ms = reduce_max(ms, world, True)
+    net = Net(workload, batch, wd)
+    net.warm()
+    sampler.wait_first(5.0)
+
+    # ---- device-timed runs (inputs resident in HBM): `blocks` regions of exactly `steps` passes ----
     barrier(world, True)
+    block_ms, launches = net.time_blocks(args.warmup, args.steps, args.blocks)
+    clocks = sampler.stop()
+    block_max = [reduce_max(t, world, True) for t in block_ms]
+    barrier(world, True)
+    ms, max_ms = float(np.median(block_ms)), float(np.median(block_max))
 
     # ---- end to end through the public API: host input -> H2D -> run -> D2H result ----
-    order = [api.BATCH, api.OUT_C, api.OUT_H, api.OUT_W] if seq == 0 else [api.BATCH, api.MAT_N, api.MAT_M]
-    for _ in range(2):
-        rpool.add(nasm, x); group.run(); group.wait(nasm); group.stop(); out = nasm.result(order)
+    net.e2e_serial(2)
     barrier(world, True)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        rpool.add(nasm, x)            # rpool_add_nasm_raw_input: host -> device copy of this step's input
-        group.run()
-        group.wait(nasm)
-        group.stop()
-        out = nasm.result(order)      # dse_get_nasm_result: device -> host read of the step's result
-    serial_ms = (time.perf_counter() - t0) * 1e3
-    serial_max = reduce_max(serial_ms, world, True)
+    serial_max = reduce_max(net.e2e_serial(args.steps), world, True)
     barrier(world, True)
-    assert np.isfinite(out).all()
-
-    # Same calls, two graphs of the same network in flight (the serving loop of a user who double-buffers):
-    # while the scheduler kernel works on one graph, the next step's input uploads and the previous step's
-    # result downloads on the library's transfer stream.  Every timed iteration still contains one
-    # host -> device input copy, one completed graph and one device -> host result read.
-    L.aspen_b200_set_tile_quanta(q_h, q_w, 100000000)
-    nasm2 = api.Nasm(dnn, batch, seq, min_ninst)
-    L.aspen_b200_set_tile_profile(0)
-    pair = [nasm, nasm2]
-    for n_ in pair:                                           # both images built and warm
-        rpool.add(n_, x); group.run(); group.wait(n_); group.stop(); out = n_.result(order)
-    cur = 0
+    net.e2e_overlapped(3)
     barrier(world, True)
-    t0 = time.perf_counter()
-    rpool.add(pair[cur], x); group.run()      # step 1 starts inside the timed region
-    for _ in range(args.steps - 1):
-        nxt = cur ^ 1
-        rpool.add(pair[nxt], x)       # upload of the next step's input, under the current graph's kernel
-        group.wait(pair[cur])
-        group.stop()
-        group.run()                   # next graph starts
-        out = pair[cur].result(order) # result of the finished graph, under the next graph's kernel
-        cur = nxt
-    group.wait(pair[cur]); group.stop(); out2 = pair[cur].result(order)
-    e2e_ms = (time.perf_counter() - t0) * 1e3     # exactly `steps` uploads, runs and downloads
-    if args.steps < 2:
-        out = out2
-    e2e_max = reduce_max(e2e_ms, world, True)
+    e2e_max = reduce_max(net.e2e_overlapped(args.steps), world, True)
     barrier(world, True)
-    assert np.isfinite(out).all() and np.array_equal(out, out2)
+    out = net.out
 
     # Extra, not the headline: both graphs armed in ONE scheduler launch (the reference's co-inference: several
     # nasms in one rpool).  Twice the ready tiles per layer for the same 148 SMs.
+    for n_ in net.nasms:
+        net.rpool.add(n_, net.x)
     co_iters = max(args.steps // 2, 1)
-    co_ms, _ = group.time_runs(2, co_iters)
-    co_max = reduce_max(co_ms, world, True)
-    co_value = 2 * batch * co_iters * world / (co_max * 1e-3)
+    co_ms, _ = net.group.time_runs(2, co_iters)
+    co_value = 2 * batch * co_iters * world / (reduce_max(co_ms, world, True) * 1e-3)
     barrier(world, True)
 
+    extras = {}
+    if not args.no_extras:
+        extras = extra_legs(args, rank, world, wd, net, workload)
+
     if rank == 0:
-        report(args, world, workload, batch, seq, nasm, flops, arena_bytes, ms, max_ms, e2e_max, serial_max, launches, clocks, x, out, cfg, wfile, wd, co_value)
-    group.close(); nasm2.close(); nasm.close(); rpool.close(); dnn.close()
+        report(args, world, workload, batch, net, ms, max_ms, block_max, e2e_max, serial_max, launches, clocks, out, wd, co_value, extras)
+    net.close()
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
 
 
-def report(args, world, workload, batch, seq, nasm, flops, arena_bytes, ms, max_ms, e2e_max, serial_max, launches, clocks, x, out, cfg, wfile, wd, co_value):
-    from aspen_b200 import api
+def strong_shard(global_batch: int, rank: int, world: int):
+    """Samples [lo, hi) of the global batch that rank `rank` of `world` computes (configs[1]: 32 -> 32 / N per GPU)."""
+    per = global_batch // world
+    return [rank * per, (rank + 1) * per]
+
+
+def by_model_assignment(rank: int, world: int):
+    """configs[2]: ResNet-50 batch 16 on the first half of the GPUs, VGG-16 batch 16 on the second half; each model's
+    batch is split evenly over its GPUs.  Returns (network, samples on this rank)."""
+    if world < 2:
+        return None
+    half = world // 2
+    return ["resnet50", 16 // half] if rank < half else ["vgg16", 16 // (world - half)]
+
+
+def gather_objects(obj, world: int):
+    if world == 1:
+        return [obj]
+    import torch.distributed as dist
+    parts = [None] * world
+    dist.all_gather_object(parts, obj)
+    return parts
+
+
+def extra_legs(args, rank, world, wd, net, workload):
+    """The other half of the metric (BERT-base batch 32) and the two multi-GPU splits the configurations name."""
+    extras = {}
+    steps = args.steps
+    # ---- BERT-base S128 batch 32 per GPU (configs[3]) ----
+    if workload == "resnet50":
+        b = Net("bert_base", WORKLOADS["bert_base"][1], wd)
+        b.warm()
+        barrier(world, True)
+        bms, _ = b.time_blocks(3, steps, 3)
+        bmax = float(np.median([reduce_max(t, world, True) for t in bms]))
+        b.e2e_overlapped(3)
+        barrier(world, True)
+        be2e = reduce_max(b.e2e_overlapped(steps), world, True)
+        barrier(world, True)
+        tf = b.flops * steps / (float(np.median(bms)) * 1e-3) / 1e12
+        extras["bert_base"] = {"metric": "sequences_per_sec", "config": {"workload": "bert_base_s128_bs32_per_gpu", "tile_quanta": list(b.tiling[:2]),
+                                                                          "min_ninst_per_ldata": b.tiling[2], "tiles": b.nasms[0].num_ninst},
+                               "value": job_value(b.batch, steps, world, bmax), "unit": "seq/s", "ms_per_step": bmax / steps,
+                               "e2e": {"value": job_value(b.batch, steps, world, be2e), "unit": "seq/s", "h2d_bytes_per_step": int(b.x.nbytes),
+                                       "d2h_bytes_per_step": int(b.out.nbytes)},
+                               "achieved_tflops": tf, "flops_per_step": b.flops}
+        b.close()
+    # ---- strong scaling (configs[1]): the global batch of 32 split 32 / N per GPU, results gathered on rank 0 ----
+    gb = WORKLOADS[workload][1]
+    if world > 1 and gb % world == 0:
+        lo, hi = strong_shard(gb, rank, world)
+        s = Net(workload, hi - lo, wd, graphs=1, min_ninst=100)
+        rows = net.x.shape[0] // gb
+        s.x_pinned.copy_(net.x_pinned[lo * rows:hi * rows])       # this rank's samples of the global batch
+        s.warm()
+        barrier(world, True)
+        sms, _ = s.time_blocks(3, steps, 3)
+        smax = float(np.median([reduce_max(t, world, True) for t in sms]))
+        barrier(world, True)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            s.e2e_serial(1)
+        se2e = reduce_max((time.perf_counter() - t0) * 1e3, world, True)
+        local = s.out.reshape(hi - lo, -1)
+        whole = gather_rows(local, world)
+        ok = None
+        if rank == 0:
+            want = net.out.reshape(gb, -1)
+            ok = bool(whole.shape == want.shape and np.abs(whole - want).max() <= 2e-3 * np.abs(want).max()
+                      and (whole.argmax(1) == want.argmax(1)).all())
+        extras["strong"] = {"config": {"workload": f"{workload}_global_bs{gb}", "per_gpu_batch": hi - lo, "tiles_per_gpu": s.nasms[0].num_ninst},
+                            "value": gb * steps / (smax * 1e-3), "unit": "inf/s", "ms_per_step": smax / steps, "scaling": "strong",
+                            "e2e_value": gb * steps / (se2e * 1e-3), "gathered_equals_single_gpu_batch": ok}
+        s.close()
+    # ---- by model (configs[2]): ResNet-50 batch 16 on one half of the GPUs, VGG-16 batch 16 on the other ----
+    assign = by_model_assignment(rank, world)
+    if assign and assign[1] >= 1:
+        name, nb = assign
+        m = Net(name, nb, wd, graphs=1, min_ninst=100 if nb < 16 else None)
+        m.warm()
+        barrier(world, True)
+        mms, _ = m.time_blocks(3, steps, 3)
+        mmax = float(np.median([reduce_max(t, world, True) for t in mms]))
+        barrier(world, True)
+        mine = gather_objects((name, nb, float(np.median(mms)) / steps), world)
+        extras["by_model"] = {"config": {"workload": "resnet50_bs16_plus_vgg16_bs16", "assignment": [[p[0], p[1]] for p in mine]},
+                              "value": 32 * steps / (mmax * 1e-3), "unit": "inf/s", "ms_per_step": mmax / steps,
+                              "ms_per_step_per_rank": [p[2] for p in mine]}
+        m.close()
+    return extras
+
+
+def report(args, world, workload, batch, net, ms, max_ms, block_max, e2e_max, serial_max, launches, clocks, out, wd, co_value, extras):
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except Exception:
         pass
+    seq, flops, nasm = net.seq, net.flops, net.nasms[0]
     peak_tf = float(peaks.get("bf16_tflops_sustained", 0) or 0) or 1400.0
     peak_src = "of measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "of fallback (1.4 PFLOP/s sustained bf16)"
     achieved_tf = flops * args.steps / (ms * 1e-3) / 1e12
     value = job_value(batch, args.steps, world, max_ms)
+    spread = (max(block_max) - min(block_max)) / max_ms if block_max else 0.0
     line = {
         "metric": "inferences_per_sec", "value": value, "unit": "inf/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": max_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32",
         "data": "synthetic",
         "config": {"workload": f"{workload}_bs{batch}_per_gpu", "seq_len": seq or None, "tile_profile": "b200 tensor-core quanta",
-                   "tile_quanta": list(TILING[workload][:2]), "min_ninst_per_ldata": TILING[workload][2], "tiles": nasm.num_ninst, "flops_per_step": flops,
-                   "l2": f"no flush: each step streams a {arena_bytes / 1e9:.2f} GB activation arena (> 126 MB L2)"},
+                   "tile_quanta": list(net.tiling[:2]), "min_ninst_per_ldata": net.tiling[2], "tiles": nasm.num_ninst, "flops_per_step": flops,
+                   "l2": f"no flush: each step streams a {net.arena_bytes / 1e9:.2f} GB activation arena (> 126 MB L2)"},
+        "timing": {"blocks": len(block_max), "block_ms": [round(t, 4) for t in block_max], "reported": "median block", "spread_frac": spread},
         "clocks": clocks,
-        "e2e": {"value": job_value(batch, args.steps, world, e2e_max), "unit": "inf/s", "h2d_bytes_per_step": int(x.nbytes),
+        "e2e": {"value": job_value(batch, args.steps, world, e2e_max), "unit": "inf/s", "h2d_bytes_per_step": int(net.x.nbytes),
                 "d2h_bytes_per_step": int(out.nbytes), "ms_per_step": e2e_max / args.steps,
                 "mode": "two graphs in flight: input upload and result download overlap the other graph's kernel",
                 "serial_value": job_value(batch, args.steps, world, serial_max), "serial_ms_per_step": serial_max / args.steps},
@@ -355,16 +557,28 @@ def report(args, world, workload, batch, seq, nasm, flops, arena_bytes, ms, max_
                          "note": "two batch-sized graphs of the network in one rpool and one scheduler launch, inputs resident"},
         "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
                      "traffic": TRAFFIC_BYTES.get(workload), "peak_source": peak_src,
-                     "note": "kernel = persistent scheduler_kernel<true> (whole tile graph, all layer types); operands are TF32, whose dense "
-                             "peak is half the bf16 figure used as denominator"},
+                     "note": "kernel = persistent scheduler_kernel<true> (whole tile graph, all layer types); operands are TF32: see peak_tf32"},
     }
+    if world == 1:
+        try:
+            tf32 = measure_matmul_peaks()
+            line["roofline"]["peak_tf32"] = tf32
+            line["roofline"]["frac_tf32"] = achieved_tf / tf32["tf32_tflops_sustained"]
+            if "bert_base" in extras:
+                extras["bert_base"]["roofline"] = {"bound": "tensor", "achieved": extras["bert_base"]["achieved_tflops"], "peak": peak_tf, "unit": "TFLOP/s",
+                                                   "frac": extras["bert_base"]["achieved_tflops"] / peak_tf,
+                                                   "frac_tf32": extras["bert_base"]["achieved_tflops"] / tf32["tf32_tflops_sustained"]}
+        except Exception as exc:  # noqa: BLE001
+            line["roofline"]["peak_tf32"] = f"not measured: {exc}"
+    line.update(extras)
     if not args.no_cpu_baseline and world == 1:
         from oracle import ref
         if ref.available():
             try:
-                rate, cores = cpu_reference_rate(workload, cfg, wfile, 4, 10, 2, wd)
+                passes = 8
+                rate, cores = cpu_reference_rate(workload, net.cfg, net.wfile, batch, passes, 2, wd)
                 line["cpu_baseline"] = {"value": rate, "unit": "inf/s", "cores": cores, "kind": "reference",
-                                        "sample": f"reference DSE path ({cores} pthread workers), 10 timed passes of a batch-4 graph of the same network"}
+                                        "sample": f"reference DSE path ({cores} pthread workers), {passes} timed passes of one batch-{batch} graph of the same network"}
             except Exception as exc:  # noqa: BLE001
                 line["cpu_baseline"] = {"value": None, "unit": "inf/s", "cores": 0, "kind": "reference", "sample": f"failed: {exc}"}
         else:

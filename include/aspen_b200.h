@@ -212,6 +212,28 @@ double aspen_b200_group_time_runs(dse_group_t *dse_group, unsigned int warmup, u
  * executor warps waited for a tile.  Returns 0, or -1 when inactive. */
 int aspen_b200_group_profile(dse_group_t *dse_group, unsigned long long *out, unsigned int *n_ctas);
 
+/* No counterpart in the reference: its transformer cfgs start at the hidden states ([net] M=768; ref
+ * files/bert_base/bert_base_aspen.cfg, files/gpt2_124M/gpt2_124M_aspen.cfg) and leave the embedding lookup to the
+ * caller.  aspen_b200_dnn_set_embedding registers the tables of a dnn (host pointers, copied): token_table
+ * [vocab][M] and position_table [max_pos][M] or NULL, M = the width of the dnn's first layer; call it before the
+ * dnn's first graph is uploaded.  aspen_b200_rpool_add_nasm_tokens then stands in for rpool_add_nasm_raw_input:
+ * token_ids is a host array [batch][seq] of int32; column b * seq + s of layer 0 becomes
+ * token_table[id] + position_table[s], gathered on the device.  The rpool must already belong to a dse group.
+ * A tied output head needs nothing new: it is a [matmul] layer whose weights are the token table (M = vocab). */
+int aspen_b200_dnn_set_embedding(aspen_dnn_t *dnn, const float *token_table, unsigned int vocab, const float *position_table,
+                                 unsigned int max_pos);
+void aspen_b200_rpool_add_nasm_tokens(rpool_t *rpool, nasm_t *nasm, const int *token_ids);
+
+/* No counterpart in the reference, whose DSEs free a layer's buffer once its child layers are complete
+ * (ref src/dse.c:84-92), so that only the last layer can be read after a run.  This library keeps every layer
+ * readable by default (dse_get_ldata_result on any layer).  keep = 0 gives that up for the layers whose output
+ * only feeds a residual add fused into their own epilogue (the expand convolutions of ResNet bottlenecks, the
+ * attention / FFN output projections of a transformer): their pre-add values are then never written to memory;
+ * reading such a layer afterwards returns zeros or stale data.  Every other layer, and the result, are unchanged
+ * bit for bit.  Applies to graphs whose device image is built after the call (first rpool_add_nasm on a group);
+ * the environment variable ASPEN_B200_HIDDEN_STATES=0 selects the same for programs that cannot call this. */
+void aspen_b200_set_hidden_states(int keep);
+
 /* No counterpart in the reference.  One matmul layer, out[n][m] = act(bias[m] + sum_k w[m][k] * x[n][k])
  * in fp32 FMA arithmetic, run as 128 x 128 tiles by the same persistent scheduler kernel as every
  * other call -- but WITHOUT ALLOCATING ANYTHING.  It is for callers that are not allowed to call

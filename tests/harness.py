@@ -20,8 +20,10 @@ NETS = {
     "vgg16": ({}, "he", (2, 2)),
     "bert_base": ({}, "n002", (3, 3)),
     "gpt2_124M": ({}, "n002", (4, 4)),
+    # GPT-2 with the tail the reference's cfg leaves out: final layernorm and the 50257-row output head
+    "gpt2_lm": ({"with_lm_head": True}, "n002", (4, 4)),
 }
-_BUILDER = {"tiny_gpt": "tiny_transformer"}
+_BUILDER = {"tiny_gpt": "tiny_transformer", "gpt2_lm": "gpt2_124M"}
 
 
 def prepare(name: str, workdir: str):

@@ -21,6 +21,17 @@ def test_two_rank_launch_aggregates_the_slowest_rank():
     # fake timings: rank r takes 10 * steps * (1 + 0.1 r) ms -> the slower rank (1) sets the time
     assert abs(rec["ms_per_step"] - 11.0) < 1e-6
     assert abs(rec["value"] - 32 * 4 * 2 / (44.0e-3)) < 1e-3
+    # the two splits of the multi-GPU legs: global batch 32 cut in rank order; one network per half of the ranks
+    assert rec["strong"]["shards"] == [[0, 16], [16, 32]]
+    assert rec["by_model"]["assignment"] == [["resnet50", 16], ["vgg16", 16]]
+
+
+def test_splits_for_eight_ranks():
+    sys.path.insert(0, ROOT)
+    import bench
+    assert [bench.strong_shard(32, r, 8) for r in range(8)] == [[4 * r, 4 * r + 4] for r in range(8)]
+    assert [bench.by_model_assignment(r, 8) for r in range(8)] == [["resnet50", 4]] * 4 + [["vgg16", 4]] * 4
+    assert bench.by_model_assignment(0, 1) is None
 
 
 def test_reference_arm_runs_on_rank_zero_only():
