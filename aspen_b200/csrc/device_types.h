@@ -37,6 +37,11 @@ struct LayerDev {
     int res_act;
     unsigned res_round;
     unsigned res_elide;       // the layer's own (pre-add) output has no other reader and is not written
+    int resmap;               // tensor map of res_in (32 x 32 boxes) when the epilogue fetches it by TMA, else -1
+    // A layer whose output is the value operand of an attention_v layer also writes it transposed ([feature][token],
+    // tokens contiguous): that copy is what the attention tile's TMA reads as a K-major operand.  nullptr: no copy.
+    float *vt_out;
+    unsigned vt_ld;
 };
 
 struct TileDev {

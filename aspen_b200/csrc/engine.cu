@@ -222,6 +222,7 @@ struct DeviceNasm {
     cudaEvent_t res_ready = nullptr;    // compute stream: the run (and the gather) are complete
     bool res_valid = false;
     // A_TMA_ROWS: zero-padded [sample][PH][PW][4] copy of the input image (borders stay zero), filled after each upload
+    std::vector<float *> scratch;       // transposed copies of attention value matrices (see LayerDev::vt_out)
     float *padded_in = nullptr;
     unsigned pin_ph = 0, pin_pw = 0, pin_pad = 0, pin_ic = 0, pin_ih = 0, pin_iw = 0;
 };
@@ -273,7 +274,7 @@ Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) 
     if (env_u64("ASPEN_B200_CTAS", &v) && v > 0 && v <= (unsigned long long)e->num_sms) e->n_ctas = (unsigned)v;
     if (env_u64("ASPEN_B200_STALL_MS", &v) && v > 0) e->stall_ns = v * 1000000ull;
     if (env_u64("ASPEN_B200_PIPE_MS", &v) && v > 0) e->pipe_ns = v * 1000000ull;
-    e->smem_bytes = (precision == 0 ? (size_t)tc::STAGES * tc::STAGE_BYTES + tc::EPI_BYTES : 0) + sizeof(tc::Shared) + 1024;
+    e->smem_bytes = (precision == 0 ? (size_t)tc::STAGES * tc::STAGE_BYTES + tc::EPI_BYTES + tc::RES_BYTES : 0) + sizeof(tc::Shared) + 1024;
     bool ok = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&e->side, cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&e->io, cudaStreamNonBlocking) == cudaSuccess &&
@@ -435,6 +436,7 @@ static void fill_layer(const nasm_t *nasm, const DeviceNasm *dn, unsigned i, int
     L.seq = nasm->tr_seq_len; L.heads = p[NUM_HEAD]; L.hd = p[NUM_HEAD] ? p[NUM_HIDDEN] / p[NUM_HEAD] : 0; L.masked = p[MASKED];
     L.p_out_c = p[OUT_C]; L.p_in_c = p[IN_C]; L.p_stride = p[STRIDE];
     L.wmap = wmap_idx;
+    L.resmap = -1;
     L.bw = 128;
     switch (l.type) {
         case CONV_LAYER: case FC_LAYER: L.a_vec4 = (L.IC % 4 == 0) && (L.ld0 % 4 == 0); break;
@@ -452,6 +454,7 @@ static void free_device_nasm(DeviceNasm *dn) {
     cudaFree(dn->layers_completed); cudaFree(dn->layer_done_init); cudaFree(dn->wmaps);
     if (dn->completed_h) cudaFreeHost(dn->completed_h);
     cudaFree(dn->in_stage); cudaFree(dn->ids_stage); cudaFree(dn->res_packed); cudaFree(dn->padded_in);
+    for (float *p : dn->scratch) cudaFree(p);
     if (dn->in_consumed) cudaEventDestroy(dn->in_consumed);
     if (dn->res_ready) cudaEventDestroy(dn->res_ready);
     delete dn;
@@ -629,6 +632,27 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
                 L.a_kind = tc::A_TMA;
                 L.amap = add_map(L.in0, L.H0, W0, (cuuint64_t)L.ld0 * sizeof(float), 128);
             }
+            // The value operand W(m, k) = V[token k][feature m] is the transpose of how the value projection stores its
+            // output.  Where that projection is a tensor-core layer of this graph (it precedes this one), it writes a
+            // second, transposed copy into scratch memory, which TMA then stages like any K-major operand; otherwise the
+            // worker threads gather it element by element.
+            const char *no_vt = getenv("ASPEN_B200_NO_VT");
+            const LAYER_TYPE pt = p1 != (unsigned)-1 ? nasm->ldata[p1].layer->type : NO_LAYER_TYPE;
+            if (p1 != (unsigned)-1 && p1 < i && p1 != 0 && (pt == MATMUL_LAYER || pt == CONV_LAYER) && L.seq % 4 == 0 && !layers[p1].vt_out &&
+                !(no_vt && atoi(no_vt) != 0)) {
+                const size_t W1 = nasm->ldata[p1].out_mat_dims[OUT_W], ldt = round_up(W1, 32);
+                float *vt = nullptr;
+                CUDA_TRY(cudaMalloc(&vt, (size_t)L.H1 * ldt * sizeof(float) + 256));
+                dn->scratch.push_back(vt);
+                CUDA_TRY(cudaMemsetAsync(vt, 0, (size_t)L.H1 * ldt * sizeof(float) + 256, e->stream));
+                const int m = add_map(vt, W1, L.H1, (cuuint64_t)ldt * sizeof(float), 64);
+                if (m >= 0) {
+                    layers[p1].vt_out = vt;
+                    layers[p1].vt_ld = (unsigned)ldt;
+                    L.b_kind = tc::B_TMA_ACT;
+                    L.wmap = m;
+                }
+            }
         }
         if (L.a_kind != tc::A_GATHER && L.amap < 0) return -1;
     }
@@ -666,6 +690,12 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
             L.res_in = layers[lo].out; L.res_ld_in = layers[lo].ldc;
             L.res_out = layers[i].out; L.res_ld_out = layers[i].ldc;
             L.res_act = layers[i].act; L.res_round = layers[i].round_out;
+            // the other operand reaches the epilogue as 32 x 32 boxes by TMA (falls back to plain loads if the driver refuses the map)
+            const char *no_res_tma = getenv("ASPEN_B200_NO_RES_TMA");
+            if (layers[lo].ldc % 4 == 0 && !(no_res_tma && atoi(no_res_tma) != 0)) {
+                const int m = add_map(layers[lo].out, Q.out_mat_dims[OUT_H], Q.out_mat_dims[OUT_W], (cuuint64_t)layers[lo].ldc * sizeof(float), 32);
+                L.resmap = m >= 0 ? m : -1;
+            }
             // The producer's own (pre-add) output: the reference frees it as soon as the residual layer has read it
             // (src/dse.c:84-92).  When nothing else reads it and the caller has not asked for every hidden state,
             // it is not written at all.

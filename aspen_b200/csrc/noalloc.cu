@@ -76,7 +76,7 @@ __global__ void noalloc_setup(NoAllocScratch *s, NoAllocArgs a) {
     L.in0 = a.x; L.ld0 = a.k; L.H0 = a.k;
     L.weight = a.w; L.bias = a.bias;
     L.K = a.k; L.Kpad = a.k; L.rows = a.m;
-    L.wmap = -1; L.amap = -1; L.bw = 128;
+    L.wmap = -1; L.amap = -1; L.resmap = -1; L.bw = 128;
     L.a_vec4 = (a.k % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.w)) % 16 == 0);
     s->layer = L;
     NasmDev G;

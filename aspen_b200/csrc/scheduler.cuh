@@ -307,7 +307,7 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
     extern __shared__ unsigned char smem_raw[];
     // stage buffers need 1024-byte alignment for the 128-byte swizzle
     unsigned char *stage_mem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
-    tc::Shared *sh = reinterpret_cast<tc::Shared *>(stage_mem + (TENSOR_CORES ? tc::STAGES * tc::STAGE_BYTES + tc::EPI_BYTES : 0u));
+    tc::Shared *sh = reinterpret_cast<tc::Shared *>(stage_mem + (TENSOR_CORES ? tc::STAGES * tc::STAGE_BYTES + tc::EPI_BYTES + tc::RES_BYTES : 0u));
     const unsigned tid = threadIdx.x, warp = tid >> 5;
     const unsigned ctrl_warp = tc::NW >> 5;
     tc::PipeState ps;
@@ -315,6 +315,7 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
     if (tid == 0) {
         for (int s = 0; s < tc::STAGES; s++) { tc::mbar_init(&sh->full[s], tc::NW); tc::mbar_init(&sh->empty[s], 1u); tc::mbar_init(&sh->landed[s], 1u); }
         tc::mbar_init(&sh->accum, 1u);
+        for (unsigned w = 0; w < tc::NW / 32u; w++) tc::mbar_init(&sh->res_full[w], 1u);
         for (int k = 0; k < 2; k++) { tc::mbar_init(&sh->posted[k], 1u); tc::mbar_init(&sh->finished[k], tc::NTHREADS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         tc::fence_proxy_async_smem();

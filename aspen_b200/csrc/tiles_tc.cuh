@@ -40,7 +40,11 @@ constexpr unsigned TMA_THREAD = NW;          // lane 0 of warp 8
 constexpr unsigned MMA_THREAD = NW + 32;     // lane 0 of warp 9
 constexpr unsigned NTHREADS = NW + 64;
 constexpr unsigned TMEM_COLS = 512;
-constexpr unsigned EPI_BYTES = (NW / 32) * 4096;   // per-warp transpose staging of the epilogue
+// The epilogue's per-warp 4 KB transpose staging lives in the first 32 KB of the operand ring: all roles of the CTA move in
+// lockstep, so when a block's accumulators are complete every stage has been read and no load of the next block is issued
+// before the workers have finished (they fence the generic-proxy accesses against the next TMA writes before that barrier).
+constexpr unsigned EPI_BYTES = 0;
+constexpr unsigned RES_BYTES = (NW / 32) * 4096;   // per-warp landing slot for the other operand of a fused residual add
 
 struct Shared {
     unsigned long long full[STAGES];
@@ -51,6 +55,7 @@ struct Shared {
     unsigned long long posted[2];     // scheduler -> executors: mailbox slot holds a tile
     unsigned long long finished[2];   // executors -> scheduler: every executor thread is done with the slot's tile
     unsigned mailbox[2];
+    unsigned long long res_full[NW / 32];   // per worker warp: its residual-operand box has landed
     float partial[NW];        // K-attention row sums of the two column halves
 };
 
@@ -58,6 +63,7 @@ struct PipeState {            // identical in every thread, carried across tiles
     unsigned it = 0;          // k-chunk iterations issued so far
     unsigned acc_phase = 0;   // accumulator barrier phase
     unsigned full_phase = 0;  // MMA thread: per-stage phase bits of the "full" barriers (not every layer uses them)
+    unsigned res_uses = 0;    // worker warps: residual-operand boxes this warp has requested so far
     bool dead = false;
 };
 
@@ -263,6 +269,16 @@ __device__ __forceinline__ void store_block_residual(float *stage, const float *
     __syncwarp();
 }
 
+// Fused residual add, other operand by TMA.  The 32 (columns n) x 32 (rows m) block a warp needs for one epilogue chunk is a
+// box of the other parent's matrix; lane 0 of the warp requests it into the warp's own 4 KB slot -- the first one before
+// the block's main loop, so it lands while the MMAs run, each further one as soon as the previous has been read into
+// registers -- and every lane then reads its own column's 32 values from shared memory (the 128-byte swizzle keeps the
+// eight lanes of a quarter-warp on different banks).  The epilogue itself issues no global loads.
+__device__ __forceinline__ void residual_request(unsigned slot_addr, const void *resmap, int m0, int n0, unsigned long long *bar) {
+    mbar_arrive_expect_tx(bar, 4096u);
+    tma_load_2d(slot_addr, resmap, m0, n0, bar);
+}
+
 // ---- per-layer operand description -------------------------------------------------------------
 // How the two operands of a layer reach shared memory (chosen on the host, LayerDev::a_kind / b_kind):
 //   X side  A_GATHER     worker threads, cp.async per 16-byte piece (4-byte pieces when IC % 4 != 0): strided
@@ -332,6 +348,7 @@ __device__ __forceinline__ Operands make_operands(const LayerDev &L, const TileD
             o.xrow = L.in0 + (size_t)((b * L.heads + head) * L.seq + q0) * L.ld0; o.xld = L.ld0;
             o.ay = (int)((b * L.heads + head) * L.seq + q0);
             o.wbase = L.in1 + (size_t)b * L.seq * L.ld1 + T.pos_h; o.wld = L.ld1;
+            o.bx = (int)(b * L.seq); o.by = (int)T.pos_h;      // B_TMA_ACT: the transposed copy [feature][token]
             o.K = L.seq; o.Kpad = (L.seq + 31u) & ~31u; o.plain = true;
             break;
         }
@@ -354,10 +371,13 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
     const void *amap = a_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.amap * 128) : nullptr;
     const void *bmap = b_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.wmap * 128) : nullptr;
     const bool vec_x = L.a_vec4 != 0;
+    const bool res_tma = L.res_out != nullptr && L.resmap >= 0;
+    const void *resmap = res_tma ? (const void *)((const unsigned char *)G.wmaps + (size_t)L.resmap * 128) : nullptr;
 
     // Activations were written with ordinary (generic proxy) stores, possibly by this very CTA a moment
     // ago; TMA reads them through the async proxy.
     if (tid == TMA_THREAD && a_tma) asm volatile("fence.proxy.async.global;" ::: "memory");
+    if (res_tma && is_worker && (tid & 31u) == 0u) asm volatile("fence.proxy.async.global;" ::: "memory");
 
     const unsigned bw = L.bw;   // 128 except for convolutions whose blocks are whole output rows
     for (unsigned n0 = 0; n0 < T.tile_w; n0 += bw) {
@@ -372,6 +392,13 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
         for (unsigned ms = 0; ms < T.tile_h; ms += TMEM_COLS) {
             const unsigned cols_super = min(TMEM_COLS, T.tile_h - ms);
             unsigned arrived = ps.it;            // next iteration this worker still owes a "full" arrival for
+            // fused residual add: ask for the first chunk's block of the other operand now, it lands under the main loop
+            const unsigned wlane_base = ((tid >> 5) & 3u) * 32u;
+            const bool res_live = res_tma && is_worker && rows_valid > wlane_base;          // this warp has columns in the block
+            const unsigned res_slot = stage_base + STAGES * STAGE_BYTES + EPI_BYTES + (tid >> 5) * 4096u;
+            const int res_m0 = (int)(T.pos_h + ms), res_n0 = (int)(T.pos_w + n0 + wlane_base);
+            if (res_live && !ps.dead && half * 32u < cols_super && (tid & 31u) == 0u)
+                residual_request(res_slot, resmap, res_m0 + (int)(half * 32u), res_n0, &sh->res_full[tid >> 5]);
             for (unsigned mp = 0; mp < cols_super; mp += 256) {
                 const unsigned nb = min(256u, cols_super - mp);
                 const unsigned NB = b_tma ? ((nb + 63u) & ~63u) : ((nb + 15u) & ~15u);
@@ -546,7 +573,7 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                 // block (n = first column of this warp's 32, m = ms) of the output matrix
                 float *oblk = L.out + (size_t)(T.pos_w + n0 + lane_base) * L.ldc + T.pos_h + ms;
                 const unsigned n_valid = rows_valid > lane_base ? rows_valid - lane_base : 0u;
-                float *epi = reinterpret_cast<float *>(stage_mem + STAGES * STAGE_BYTES) + (tid >> 5) * 1024u;
+                float *epi = reinterpret_cast<float *>(stage_mem) + (tid >> 5) * 1024u;
                 float v[32];
                 if (op.softmax) {
                     // scores -> mask -> / sqrt(hd) -> exp, normalised by the column sum (ref src/tiled_kernels.c:859-876)
@@ -620,7 +647,47 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                             #pragma unroll
                             for (unsigned j = 0; j < 32; j++) v[j] = tf32_round(v[j]);
                         }
-                        if (!ps.dead) {
+                        if (L.vt_out && !ps.dead && row < rows_valid) {
+                            // transposed copy for an attention_v consumer: lanes hold consecutive columns, so each of the 32
+                            // stores of a warp covers one full 128-byte line of a feature's row
+                            float *vt = L.vt_out + (size_t)(T.pos_h + ms + c * 32u) * L.vt_ld + T.pos_w + n0 + row;
+                            #pragma unroll
+                            for (unsigned j = 0; j < 32; j++)
+                                if (j < valid) vt[(size_t)j * L.vt_ld] = v[j];
+                        }
+                        if (res_live) {
+                            // the other operand's block is in this warp's slot: own column = row `lane` of the box
+                            if (!ps.dead && !mbar_wait(&sh->res_full[tid >> 5], ps.res_uses & 1u, ctrl, status, 11)) ps.dead = true;
+                            ps.dead = __any_sync(0xffffffffu, ps.dead);
+                            ps.res_uses++;
+                            float4 r[8];
+                            const unsigned lane = tid & 31u;
+                            const float4 *slot = reinterpret_cast<const float4 *>(stage_mem + STAGES * STAGE_BYTES + EPI_BYTES + (tid >> 5) * 4096u + lane * 128u);
+                            #pragma unroll
+                            for (unsigned q = 0; q < 8; q++) r[q] = slot[q ^ (lane & 7u)];
+                            __syncwarp();
+                            if (!ps.dead && c + 2u < nchunk && lane == 0u)
+                                residual_request(res_slot, resmap, res_m0 + (int)((c + 2u) * 32u), res_n0, &sh->res_full[tid >> 5]);
+                            if (!ps.dead) {
+                                if (!L.res_elide) store_block_coalesced(epi, v, oblk + c * 32u, L.ldc, n_valid, valid);
+                                const int act2 = L.res_act;
+                                #pragma unroll
+                                for (unsigned q = 0; q < 8; q++) { v[4 * q] += r[q].x; v[4 * q + 1] += r[q].y; v[4 * q + 2] += r[q].z; v[4 * q + 3] += r[q].w; }
+                                if (act2 == RELU) {
+                                    #pragma unroll
+                                    for (unsigned j = 0; j < 32; j++) v[j] = v[j] > 0.f ? v[j] : 0.f;
+                                } else if (act2 != NO_ACTIVATION && act2 != LINEAR) {
+                                    #pragma unroll
+                                    for (unsigned j = 0; j < 32; j++) v[j] = activate(v[j], act2);
+                                }
+                                if (L.res_round) {
+                                    #pragma unroll
+                                    for (unsigned j = 0; j < 32; j++) v[j] = tf32_round(v[j]);
+                                }
+                                const size_t colg = T.pos_w + n0 + lane_base, mg = T.pos_h + ms + c * 32u;
+                                store_block_coalesced(epi, v, L.res_out + colg * L.res_ld_out + mg, L.res_ld_out, n_valid, valid);
+                            }
+                        } else if (!ps.dead) {
                             if (L.res_out) {
                                 const size_t col0 = T.pos_w + n0 + lane_base, m0 = T.pos_h + ms + c * 32u;
                                 store_block_residual(epi, v, oblk + c * 32u, L.ldc, n_valid, valid, L.res_in + col0 * L.res_ld_in + m0, L.res_ld_in,
@@ -629,6 +696,7 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
                         }
                     }
                 }
+                fence_proxy_async_smem();     // staging reads and writes of the ring's memory, before the next block's TMA writes
                 tc_fence_before();
             }
             ps.acc_phase ^= 1u;
