@@ -213,6 +213,37 @@ def tiny_transformer(masked: bool = False, pre_ln: bool = False):
     return transformer(2, 64, 4, 128, pre_ln=pre_ln, masked=masked, act="gelu_acc" if masked else "gelu")
 
 
+def single_layer(kind: str):
+    """One-layer (or one layer plus the producer it needs) networks for profiler captures of a single tile kernel:
+    the shapes are the ones ResNet-50 / BERT-base spend their time in."""
+    c = _Cfg()
+    if kind == "conv3x3":            # stage-2 3x3 convolution: K = 1152
+        c.sec("net", height=28, width=28, channels=128)
+        _conv(c, 128, 128, 3, 1, 1, "relu", bn=False)
+    elif kind == "conv1x1":          # stage-4 reduce convolution: K = 2048
+        c.sec("net", height=7, width=7, channels=2048)
+        _conv(c, 2048, 512, 1, 1, 0, "relu", bn=False)
+    elif kind == "matmul_up":        # FFN up-projection with GELU: K = 768, 3072 rows
+        c.sec("net", M=768, height=1, filters=768)
+        _matmul(c, 3072, 768, act="gelu")
+    elif kind == "matmul_down":      # FFN down-projection: K = 3072
+        c.sec("net", M=3072, height=1, filters=3072)
+        _matmul(c, 768, 3072)
+    elif kind == "residual":         # stage-1 shortcut add behind its 1x1 expand convolution
+        c.sec("net", height=56, width=56, channels=256)
+        _conv(c, 256, 256, 1, 1, 0, "linear", bn=False)
+        c.sec("shortcut", **{"from": -2}, activation="relu")
+    elif kind == "layernorm":
+        c.sec("net", M=768, height=1, filters=768)
+        _layernorm(c, 768)
+    elif kind == "maxpool":          # the 3x3 / 2 pool behind the stem
+        c.sec("net", height=112, width=112, channels=64)
+        c.sec("maxpool", size=3, stride=2, pad=1)
+    else:
+        raise ValueError(kind)
+    return c.text(), c.weighted
+
+
 BUILDERS = {
     "resnet50": resnet50,
     "vgg16": vgg16,
@@ -223,6 +254,7 @@ BUILDERS = {
     "tiny_transformer": tiny_transformer,
     "tiny_yolo": tiny_yolo,
     "tiny_acts": tiny_acts,
+    **{f"layer_{k}": (lambda k=k: single_layer(k)) for k in ("conv3x3", "conv1x1", "matmul_up", "matmul_down", "residual", "layernorm", "maxpool")},
 }
 
 
