@@ -1049,6 +1049,9 @@ int engine_stop(Engine *e) {
         cudaMemcpyAsync(&e->ctrl->stop, &one, sizeof(unsigned), cudaMemcpyHostToDevice, e->side);
     }
     cudaError_t err = cudaStreamSynchronize(e->stream);
+    // the stop write itself must have landed (or been dropped by a kernel that had already left) before the next arm
+    // kernel clears the flag: a write that arrived after it would end the next run after its first tiles
+    cudaStreamSynchronize(e->side);
     e->running = false;
     for (nasm_t *n : e->in_flight)
         if (n->dev && *(volatile unsigned *)n->dev->completed_h == 0) n->dev->armed = true;   // unfinished: restarts at the next run
