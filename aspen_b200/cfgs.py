@@ -209,8 +209,8 @@ def tiny_acts():
     return c.text(), c.weighted
 
 
-def tiny_transformer(masked: bool = False, pre_ln: bool = False):
-    return transformer(2, 64, 4, 128, pre_ln=pre_ln, masked=masked, act="gelu_acc" if masked else "gelu")
+def tiny_transformer(masked: bool = False, pre_ln: bool = False, heads: int = 4):
+    return transformer(2, 64, heads, 128, pre_ln=pre_ln, masked=masked, act="gelu_acc" if masked else "gelu")
 
 
 def single_layer(kind: str):

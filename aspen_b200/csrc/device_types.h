@@ -42,6 +42,13 @@ struct LayerDev {
     // tokens contiguous): that copy is what the attention tile's TMA reads as a K-major operand.  nullptr: no copy.
     float *vt_out;
     unsigned vt_ld;
+    // attention_v layer that computes its own probabilities (attention_k fused into it, see tc::tile_attention):
+    // tensor maps of the query and key projections; where the attention_k layer's matrix is still to be written, its
+    // address, column stride and rounding flag.
+    unsigned att_fused;
+    int att_qmap, att_kmap;
+    float *att_p_out;
+    unsigned att_p_ld, att_p_round;
 };
 
 struct TileDev {

@@ -212,6 +212,7 @@ struct DeviceNasm {
     bool armed = false;  // has input, counters will be reset at the next run
     bool round_input = false;   // tensor-core path: the input is rounded to TF32 after upload
     bool ran = false;
+    bool fused_attention = false;   // some attention_v layer computes its own probabilities: the run needs the kernel that has that tile
     // Transfers next to a running graph: only DMA goes to the transfer stream (a kernel could not start while the
     // scheduler kernel holds every SM's shared memory); the scatter of a strided input and the gather of the last
     // layer's result are kernels on the compute stream, ordered around the graph's own run.
@@ -287,6 +288,8 @@ Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) 
             ? cudaFuncSetAttribute(sched::scheduler_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes)
             : cudaFuncSetAttribute(sched::scheduler_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes);
         ok = a == cudaSuccess;
+        if (ok && precision == 0)
+            ok = cudaFuncSetAttribute(sched::scheduler_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes) == cudaSuccess;
     }
     if (ok && getenv("ASPEN_B200_PROFILE")) {
         size_t bytes = (size_t)e->n_ctas * sched::PROF_SLOTS * sizeof(unsigned long long);
@@ -667,6 +670,42 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
         }
     }
     dn->round_input = layers[0].round_out != 0;
+    // Attention fusion (tensor-core path): an attention_v layer whose probabilities come from an attention_k layer that
+    // nothing else reads computes them itself, per (sample, head, block of queries), and the seq x seq matrix never goes
+    // to memory (ref src/tiled_kernels.c:784-1038 are two layers).  Needs head sizes of 32 or 64, the TMA staging of
+    // queries, keys and the transposed values, and one head per tile row.  Where every hidden state has to stay readable
+    // the tile also writes the probabilities, which it can only do when all keys fit one group of 128.
+    // OFF unless ASPEN_B200_ATTN_FUSE=1: the fused tile itself takes 13 us where the two tiles it replaces take 20
+    // (BERT-base, 128 x 128 x 64 per head), but the kernel instantiation that contains it runs every other tile type about
+    // 1.5 x slower (its register allocation spills on the common path, and with 176 KB of shared memory per CTA little L1
+    // is left to absorb spills), a net loss for now.
+    std::vector<unsigned char> attn_bypassed(nasm->num_ldata, 0);
+    const char *want_attn = getenv("ASPEN_B200_ATTN_FUSE");
+    if (e->precision == 0 && want_attn && atoi(want_attn) != 0) {
+        for (unsigned i = 1; i < nasm->num_ldata; i++) {
+            if (nasm->ldata[i].layer->type != V_ATTENTION_LAYER) continue;
+            LayerDev &V = layers[i];
+            const unsigned k = nasm->ldata[i].parent_ldata_idx_arr[PARENT_0];
+            if (k == (unsigned)-1 || nasm->ldata[k].layer->type != K_ATTENTION_LAYER) continue;
+            const LayerDev &K = layers[k];
+            bool only_reader = true;
+            for (unsigned j = 1; j < nasm->num_ldata; j++)
+                if (j != i && (nasm->ldata[j].parent_ldata_idx_arr[PARENT_0] == k || nasm->ldata[j].parent_ldata_idx_arr[PARENT_1] == k)) only_reader = false;
+            const bool keep = keep_hidden_states();
+            if (!only_reader || k == nasm->num_ldata - 1) continue;
+            if (V.b_kind != tc::B_TMA_ACT || V.a_kind != tc::A_TMA || K.a_kind != tc::A_TMA || K.b_kind != tc::B_TMA_ACT) continue;
+            if ((V.hd != 32 && V.hd != 64) || K.hd != V.hd || K.heads != V.heads) continue;
+            if (nasm->ldata[i].ninst_tile_dims[OUT_H] != V.hd || nasm->ldata[i].ninst_tile_dims[OUT_W] > 128 || V.seq % nasm->ldata[i].ninst_tile_dims[OUT_W] != 0) continue;
+            if (keep && V.seq > 128) continue;
+            V.att_fused = 1;
+            V.att_qmap = K.amap;
+            V.att_kmap = K.wmap;
+            V.masked = K.masked;
+            if (keep) { V.att_p_out = K.out; V.att_p_ld = K.ldc; V.att_p_round = K.round_out; }
+            attn_bypassed[k] = 1;
+            dn->fused_attention = true;
+        }
+    }
     // Residual fusion (tensor-core path): a residual layer whose later parent is a convolution or a matmul
     // is computed in that parent's epilogue, which then needs the earlier parent's tiles of the same region
     // (fused_other[producer] = that layer).  The residual layer's own tiles stay in the graph and only pass
@@ -731,7 +770,7 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
         T.pos_h = ni.out_mat_pos[OUT_H]; T.pos_w = ni.out_mat_pos[OUT_W];
         T.tile_h = ni.tile_dims[OUT_H]; T.tile_w = ni.tile_dims[OUT_W];
         T.need = (unsigned)(ni.parent_ninst_idx.size() + ni.extra_parent_idx.size());
-        T.flags = written_by_parents[T.layer] ? TILE_WRITTEN_BY_PARENTS : 0u;
+        T.flags = (written_by_parents[T.layer] || attn_bypassed[T.layer]) ? TILE_WRITTEN_BY_PARENTS : 0u;
         if (fused_other[T.layer] != (unsigned)-1) {
             // the fused residual reads the other parent over this tile's own region: tiles of that layer's grid
             // (rows fastest) that overlap it become parents too
@@ -997,7 +1036,11 @@ static int launch_run(Engine *e, const std::vector<nasm_t *> &run) {
     unsigned arm_blocks = std::min<unsigned>((total + 255) / 256, 1024);
     sched::arm_kernel<<<arm_blocks, 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue, total, n_init, n_input, e->stall_ns, e->pipe_ns);
     sched::seed_kernel<<<std::max(1u, std::min<unsigned>((n_init + 255) / 256, 256)), 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue);
-    if (e->precision == 0)
+    bool any_attention = false;
+    for (nasm_t *nasm : run) any_attention |= nasm->dev->fused_attention;
+    if (e->precision == 0 && any_attention)
+        sched::scheduler_kernel<true, true><<<e->n_ctas, sched::SCHED_THREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
+    else if (e->precision == 0)
         sched::scheduler_kernel<true><<<e->n_ctas, sched::SCHED_THREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
     else
         sched::scheduler_kernel<false><<<e->n_ctas, sched::SCHED_THREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);

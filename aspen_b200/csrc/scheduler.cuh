@@ -130,13 +130,25 @@ static __global__ void seed_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queu
     }
 }
 
-template <bool TENSOR_CORES>
+template <bool TENSOR_CORES, bool ATTENTION>
 __device__ __forceinline__ void run_tile(const LayerDev &L, const TileDev &T, const NasmDev &G, unsigned char *stage_mem, tc::Shared *sh,
                                          tc::PipeState &ps, CtrlDev *ctrl, StatusHost *status) {
     const unsigned tid = threadIdx.x;
     switch (L.type) {
         case CONV_LAYER: case FC_LAYER: case MATMUL_LAYER: case K_ATTENTION_LAYER: case V_ATTENTION_LAYER:
-            if (TENSOR_CORES) tc::tile_gemm(L, T, G, stage_mem, sh, ps, ctrl, status);
+            if (TENSOR_CORES && ATTENTION && L.att_fused) {
+                tc::AttnArgs a;
+                a.seq = L.seq; a.hd = L.hd; a.heads = L.heads; a.masked = L.masked; a.ldc = L.ldc; a.round_out = L.round_out;
+                a.att_p_ld = L.att_p_ld; a.att_p_round = L.att_p_round; a.out = L.out; a.att_p_out = L.att_p_out;
+                a.qmap = (const unsigned char *)G.wmaps + (size_t)L.att_qmap * 128;
+                a.kmap = (const unsigned char *)G.wmaps + (size_t)L.att_kmap * 128;
+                a.vmap = (const unsigned char *)G.wmaps + (size_t)L.wmap * 128;
+                tc::AttnPipe ap;
+                ap.att_tiles = ps.att_tiles; ap.att_groups = ps.att_groups; ap.dead = ps.dead;
+                ps.dead = tc::tile_attention(a, T, stage_mem, sh, ap, ctrl, status);
+                ps.att_tiles++;
+                ps.att_groups += tc::attention_groups(L.seq, L.masked, T);
+            } else if (TENSOR_CORES) tc::tile_gemm(L, T, G, stage_mem, sh, ps, ctrl, status);
             else if (tid < tc::NW) tile_gemm_ffma(L, T, tid, tc::NW);
             break;
         case RESIDUAL_LAYER: if (tid < tc::NW) tile_residual(L, T, tid, tc::NW); break;
@@ -301,7 +313,10 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
     if (lane == 0) { sh->mailbox[issued & 1u] = ASPEN_TILE_NONE; tc::mbar_arrive(&sh->posted[issued & 1u]); }
 }
 
-template <bool TENSOR_CORES>
+// ATTENTION: the instantiation that contains the fused attention tile.  It is a kernel of its own because the mere presence
+// of that code changes the register allocation of the contraction tile's main loop (measured: the whole kernel 40 % slower);
+// graphs without a fused attention layer run the instantiation without it.
+template <bool TENSOR_CORES, bool ATTENTION = false>
 __global__ void __launch_bounds__(SCHED_THREADS, 1)
 scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHost *status, unsigned long long *prof) {
     extern __shared__ unsigned char smem_raw[];
@@ -316,6 +331,8 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
         for (int s = 0; s < tc::STAGES; s++) { tc::mbar_init(&sh->full[s], tc::NW); tc::mbar_init(&sh->empty[s], 1u); tc::mbar_init(&sh->landed[s], 1u); }
         tc::mbar_init(&sh->accum, 1u);
         for (unsigned w = 0; w < tc::NW / 32u; w++) tc::mbar_init(&sh->res_full[w], 1u);
+        tc::mbar_init(&sh->att_q, 1u); tc::mbar_init(&sh->att_k, 1u); tc::mbar_init(&sh->att_v, 1u);
+        tc::mbar_init(&sh->att_s, 1u); tc::mbar_init(&sh->att_p, tc::NW); tc::mbar_init(&sh->att_o, 1u);
         for (int k = 0; k < 2; k++) { tc::mbar_init(&sh->posted[k], 1u); tc::mbar_init(&sh->finished[k], tc::NTHREADS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         tc::fence_proxy_async_smem();
@@ -348,7 +365,7 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
             const NasmDev &G = nasms[g];
             const TileDev T = G.tiles[gid - G.tile_base];
             const LayerDev &L = G.layers[T.layer];
-            run_tile<TENSOR_CORES>(L, T, G, stage_mem, sh, ps, ctrl, status);
+            run_tile<TENSOR_CORES, ATTENTION>(L, T, G, stage_mem, sh, ps, ctrl, status);
             if (my_prof && tid == 0) {
                 unsigned long long now = global_ns();
                 my_prof[2 + T.layer % PROF_LAYERS] += now - t_mark; my_prof[2 + PROF_LAYERS + T.layer % PROF_LAYERS] += 1ull; t_mark = now;

@@ -30,7 +30,7 @@
 
 namespace tc {
 
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
 constexpr int LAG = 2;                       // cp.async groups a worker keeps in flight
 constexpr unsigned A_STAGE_BYTES = 128 * 128;
 constexpr unsigned B_STAGE_BYTES = 256 * 128;
@@ -56,6 +56,9 @@ struct Shared {
     unsigned long long finished[2];   // executors -> scheduler: every executor thread is done with the slot's tile
     unsigned mailbox[2];
     unsigned long long res_full[NW / 32];   // per worker warp: its residual-operand box has landed
+    // fused attention tile: queries / a key group / a value group have landed (TMA), the scores of a group are complete
+    // (tcgen05.commit), the workers have written the group's probabilities to shared memory, the group's P x V MMAs are complete
+    unsigned long long att_q, att_k, att_v, att_s, att_p, att_o;
     float partial[NW];        // K-attention row sums of the two column halves
 };
 
@@ -64,6 +67,7 @@ struct PipeState {            // identical in every thread, carried across tiles
     unsigned acc_phase = 0;   // accumulator barrier phase
     unsigned full_phase = 0;  // MMA thread: per-stage phase bits of the "full" barriers (not every layer uses them)
     unsigned res_uses = 0;    // worker warps: residual-operand boxes this warp has requested so far
+    unsigned att_tiles = 0, att_groups = 0;   // fused attention tiles / key groups completed so far (barrier phases)
     bool dead = false;
 };
 
@@ -706,6 +710,186 @@ static __device__ void tile_gemm(const LayerDev L, const TileDev T, const NasmDe
             if (tid == MMA_THREAD) tc_fence_after();
         }
     }
+}
+
+// ---- attention_k + attention_v as ONE tile -------------------------------------------------------------
+// An attention_v tile -- one head's features for up to 128 queries of one sample -- computes its own probabilities
+// instead of reading them back (ref src/tiled_kernels.c:784-932 and 934-1038 are two layers with the seq x seq matrix
+// between them).  Per group of 128 keys:
+//     S = Q K^T           tcgen05.mma, M = 128 queries, N = 128 keys, K = head size; Q and K by TMA from the projections
+//     e = exp(mask(S) / sqrt(hd))   by the thread that owns the query row, straight from TMEM; row sums stay in registers
+//     P (TF32, unnormalised) -> shared memory in the K-major swizzled operand layout
+//     O += P V            tcgen05.mma, M = 128, N = head size, K = 128 keys; V by TMA from the transposed copy
+// and at the end O / rowsum is stored.  The reference's softmax subtracts no maximum, so groups need no rescaling.
+// With a causal mask the groups that lie entirely above the tile's queries are skipped.  When every hidden state must
+// stay readable (the host allows that with one key group only) the normalised probabilities are also written to the
+// attention_k layer's matrix, recomputed from the scores that are still in TMEM.
+// The operand ring (and the residual slots behind it) is carved up for this tile: Q 32 KB | K 32 KB | P 64 KB | V 32 KB;
+// the epilogue's transpose staging reuses the Q buffer, which nothing reads once the last MMA has completed.
+// Every barrier completes once per key group (att_q once per tile), in order, so the parity of a completion follows from
+// counts every thread keeps: no role has to track which barriers it waited on.
+constexpr unsigned ATT_Q = 0u, ATT_K = 32768u, ATT_P = 65536u, ATT_V = 131072u, ATT_EPI = 0u;
+static_assert(ATT_V + 32768u <= STAGES * STAGE_BYTES + RES_BYTES, "the attention tile's buffers must fit the ring plus the residual slots");
+constexpr unsigned ATT_ACC_O = 256u;      // TMEM column of the output accumulator (scores use columns 0..127)
+
+// The function is deliberately NOT inlined into the persistent kernel and takes everything by value: inlined, its register
+// needs pushed the contraction tile's main loop into spills (the whole kernel ran 45 % slower, attention layer or not); a
+// call that takes references to the kernel's own state forces that state into local memory (worse still).  It returns the
+// `dead` flag; the caller advances the two phase counters.
+struct AttnArgs {     // what the tile needs of its layer descriptor
+    unsigned seq, hd, heads, masked, ldc, round_out, att_p_ld, att_p_round;
+    float *out, *att_p_out;
+    const void *qmap, *kmap, *vmap;
+};
+struct AttnPipe { unsigned att_tiles, att_groups; bool dead; };
+
+static __device__ __noinline__ bool tile_attention(const AttnArgs L, const TileDev T, unsigned char *stage_mem, Shared *sh,
+                                                   AttnPipe ps, CtrlDev *ctrl, StatusHost *status) {
+    const unsigned tid = threadIdx.x;
+    const bool is_worker = tid < NW;
+    const unsigned row = tid & 127u, half = (tid >> 7) & 1u;
+    const unsigned base = smem_u32(stage_mem), tmem = sh->tmem_base;
+    const unsigned seq = L.seq, hd = L.hd, qchunks = hd >> 5;
+    const unsigned b = T.pos_w / seq, q0 = T.pos_w - b * seq, head = T.pos_h / hd;
+    const unsigned nq = T.tile_w;
+    const void *qmap = L.qmap, *kmap = L.kmap, *vmap = L.vmap;
+    // key groups of 128; with a causal mask nothing beyond the last query's own position contributes
+    const unsigned last_key = L.masked ? min(seq, q0 + nq) : seq;
+    const unsigned groups = (last_key + 127u) >> 7;
+    const float inv_scale = 1.f / sqrtf((float)hd);
+    const unsigned lane_base = ((tid >> 5) & 3u) * 32u;
+    const unsigned q = q0 + row;
+    float rowsum = 0.f;
+    // parity of the completion that belongs to key group g of THIS tile
+    #define ATT_PAR(g) ((ps.att_groups + (g)) & 1u)
+
+    if (tid == TMA_THREAD) asm volatile("fence.proxy.async.global;" ::: "memory");
+    for (unsigned g = 0; g < groups; g++) {
+        const unsigned key0 = g << 7;
+        if (tid == TMA_THREAD) {
+            if (g == 0 && !ps.dead) {
+                mbar_arrive_expect_tx(&sh->att_q, qchunks * A_STAGE_BYTES);
+                for (unsigned c = 0; c < qchunks; c++)
+                    tma_load_2d(base + ATT_Q + c * A_STAGE_BYTES, qmap, (int)(head * hd + c * 32u), (int)(b * seq + q0), &sh->att_q);
+            }
+            // the key buffer is free once the previous group's scores are complete, the value buffer once its P x V is
+            if (g > 0 && !ps.dead && !mbar_wait(&sh->att_s, ATT_PAR(g - 1u), ctrl, status, 12)) ps.dead = true;
+            if (!ps.dead) {
+                mbar_arrive_expect_tx(&sh->att_k, qchunks * A_STAGE_BYTES);
+                for (unsigned c = 0; c < qchunks; c++)
+                    for (unsigned j = 0; j < 128u; j += 64u)
+                        tma_load_2d(base + ATT_K + c * A_STAGE_BYTES + j * 128u, kmap, (int)(head * hd + c * 32u), (int)(b * seq + key0 + j), &sh->att_k);
+            }
+            if (g > 0 && !ps.dead && !mbar_wait(&sh->att_o, ATT_PAR(g - 1u), ctrl, status, 13)) ps.dead = true;
+            if (!ps.dead) {
+                mbar_arrive_expect_tx(&sh->att_v, 4u * 8192u);
+                for (unsigned c = 0; c < 4u; c++)
+                    tma_load_2d(base + ATT_V + c * 8192u, vmap, (int)(b * seq + key0 + c * 32u), (int)T.pos_h, &sh->att_v);
+            }
+        } else if (tid == MMA_THREAD) {
+            if (g == 0 && !ps.dead && !mbar_wait(&sh->att_q, ps.att_tiles & 1u, ctrl, status, 14)) ps.dead = true;
+            if (!ps.dead && !mbar_wait(&sh->att_k, ATT_PAR(g), ctrl, status, 15)) ps.dead = true;
+            if (!ps.dead) {
+                tc_fence_after();
+                const unsigned idesc = umma_idesc(128u);
+                for (unsigned c = 0; c < qchunks; c++) {
+                    const unsigned long long adesc = umma_desc(base + ATT_Q + c * A_STAGE_BYTES), bdesc = umma_desc(base + ATT_K + c * A_STAGE_BYTES);
+                    #pragma unroll
+                    for (unsigned k8 = 0; k8 < 4; k8++) tc_mma_tf32(tmem, adesc + 2ull * k8, bdesc + 2ull * k8, idesc, (c | k8) != 0u);
+                }
+                tc_commit(&sh->att_s);
+            }
+            // probabilities of the group in shared memory (the workers have also finished reading the scores), values landed
+            if (!ps.dead && !mbar_wait(&sh->att_p, ATT_PAR(g), ctrl, status, 16)) ps.dead = true;
+            if (!ps.dead && !mbar_wait(&sh->att_v, ATT_PAR(g), ctrl, status, 17)) ps.dead = true;
+            if (!ps.dead) {
+                tc_fence_after();
+                const unsigned idesc = umma_idesc(hd);
+                for (unsigned c = 0; c < 4u; c++) {
+                    const unsigned long long adesc = umma_desc(base + ATT_P + c * A_STAGE_BYTES), bdesc = umma_desc(base + ATT_V + c * 8192u);
+                    #pragma unroll
+                    for (unsigned k8 = 0; k8 < 4; k8++) tc_mma_tf32(tmem + ATT_ACC_O, adesc + 2ull * k8, bdesc + 2ull * k8, idesc, (g | c | k8) != 0u);
+                }
+                tc_commit(&sh->att_o);
+            }
+        } else if (is_worker) {
+            if (!ps.dead && !mbar_wait(&sh->att_s, ATT_PAR(g), ctrl, status, 18)) ps.dead = true;
+            // the previous group's P x V must have read the probability buffer before it is overwritten
+            if (g > 0 && !ps.dead && !mbar_wait(&sh->att_o, ATT_PAR(g - 1u), ctrl, status, 19)) ps.dead = true;
+            ps.dead = __any_sync(0xffffffffu, ps.dead);
+            tc_fence_after();
+            #pragma unroll 1
+            for (unsigned i = 0; i < 2; i++) {
+                const unsigned c = half + 2u * i;                                   // chunk of 32 keys inside the group
+                float v[32];
+                if (!ps.dead) tmem_ld32(tmem + (lane_base << 16) + c * 32u, v);
+                #pragma unroll
+                for (unsigned j = 0; j < 32; j++) {
+                    const unsigned key = key0 + c * 32u + j;
+                    float x = 0.f;
+                    if (key < seq) x = __expf(((L.masked && key > q) ? -1e10f : v[j]) * inv_scale);
+                    rowsum += x;
+                    v[j] = tf32_round(x);
+                }
+                float4 *dst = reinterpret_cast<float4 *>(stage_mem + ATT_P + c * A_STAGE_BYTES + row * 128u);
+                #pragma unroll
+                for (unsigned p = 0; p < 8; p++) dst[p ^ (row & 7u)] = make_float4(v[4 * p], v[4 * p + 1], v[4 * p + 2], v[4 * p + 3]);
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            if (!ps.dead) mbar_arrive(&sh->att_p);
+        }
+    }
+    if (is_worker) {
+        // row sum over both halves of the row, then the output block
+        sh->partial[tid] = rowsum;
+        worker_barrier(NW);
+        const float inv_sum = 1.f / (sh->partial[row] + sh->partial[row + 128u]);
+        if (!ps.dead && !mbar_wait(&sh->att_o, ATT_PAR(groups - 1u), ctrl, status, 20)) ps.dead = true;
+        ps.dead = __any_sync(0xffffffffu, ps.dead);
+        tc_fence_after();
+        const unsigned n_valid = nq > lane_base ? nq - lane_base : 0u;
+        float *epi = reinterpret_cast<float *>(stage_mem + ATT_EPI) + (tid >> 5) * 1024u;
+        float v[32];
+        if (half * 32u < hd) {
+            if (!ps.dead) tmem_ld32(tmem + (lane_base << 16) + ATT_ACC_O + half * 32u, v);
+            #pragma unroll
+            for (unsigned j = 0; j < 32; j++) v[j] = L.round_out ? tf32_round(v[j] * inv_sum) : v[j] * inv_sum;
+            float *oblk = L.out + (size_t)(T.pos_w + lane_base) * L.ldc + T.pos_h + half * 32u;
+            if (!ps.dead) store_block_coalesced(epi, v, oblk, L.ldc, n_valid, min(32u, T.tile_h - half * 32u));
+        }
+        if (L.att_p_out) {
+            // the attention_k layer's own matrix: column (b, head, query), rows = keys; one group, its scores are still in TMEM
+            #pragma unroll 1
+            for (unsigned c = half; c * 32u < seq; c += 2u) {
+                if (!ps.dead) tmem_ld32(tmem + (lane_base << 16) + c * 32u, v);
+                #pragma unroll
+                for (unsigned j = 0; j < 32; j++) {
+                    const unsigned key = c * 32u + j;
+                    float x = 0.f;
+                    if (key < seq) x = __expf(((L.masked && key > q) ? -1e10f : v[j]) * inv_scale) * inv_sum;
+                    v[j] = L.att_p_round ? tf32_round(x) : x;
+                }
+                float *pblk = L.att_p_out + (size_t)((b * L.heads + head) * seq + q0 + lane_base) * L.att_p_ld + c * 32u;
+                if (!ps.dead) store_block_coalesced(epi, v, pblk, L.att_p_ld, n_valid, min(32u, seq - c * 32u));
+            }
+        }
+        worker_barrier(NW);           // partial[] is reused by the next tile
+        fence_proxy_async_smem();     // generic accesses to the ring's memory, before the next tile's TMA writes
+        tc_fence_before();
+    }
+    #undef ATT_PAR
+    __syncwarp();
+    asm volatile("bar.sync 2, %0;" ::"r"(NTHREADS) : "memory");
+    if (tid == MMA_THREAD) tc_fence_after();
+    return ps.dead;
+}
+
+// Key groups the fused attention tile walks for tile T (the caller advances its phase counter by this).
+__device__ __forceinline__ unsigned attention_groups(unsigned seq, unsigned masked, const TileDev &T) {
+    const unsigned q0 = T.pos_w % seq;
+    const unsigned last_key = masked ? min(seq, q0 + T.tile_w) : seq;
+    return (last_key + 127u) >> 7;
 }
 
 }  // namespace tc

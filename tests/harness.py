@@ -13,6 +13,9 @@ NETS = {
     "tiny_cnn": ({}, "he", (11, 10)),
     "tiny_transformer": ({}, "n002", (13, 12)),
     "tiny_gpt": ({"masked": True, "pre_ln": True}, "n002", (15, 14)),
+    # head size 32: the smallest the fused attention tile takes (the 4-head variants above have head size 16)
+    "tiny_attn": ({"heads": 2}, "n002", (21, 20)),
+    "tiny_attn_causal": ({"heads": 2, "masked": True, "pre_ln": True}, "n002", (23, 22)),
     "custom": ({}, "he", (5, 6)),
     "tiny_yolo": ({}, "he", (17, 16)),
     "tiny_acts": ({}, "he", (19, 18)),
@@ -23,7 +26,7 @@ NETS = {
     # GPT-2 with the tail the reference's cfg leaves out: final layernorm and the 50257-row output head
     "gpt2_lm": ({"with_lm_head": True}, "n002", (4, 4)),
 }
-_BUILDER = {"tiny_gpt": "tiny_transformer", "gpt2_lm": "gpt2_124M"}
+_BUILDER = {"tiny_gpt": "tiny_transformer", "gpt2_lm": "gpt2_124M", "tiny_attn": "tiny_transformer", "tiny_attn_causal": "tiny_transformer"}
 
 
 def prepare(name: str, workdir: str):

@@ -68,6 +68,8 @@ CASES = [
     ("tiny_cnn", 2, 0, 20, 1, 0), ("tiny_cnn", 2, 0, 20, 0, 0), ("tiny_cnn", 5, 0, 3, 0, 1),
     ("tiny_transformer", 2, 16, 20, 1, 0), ("tiny_transformer", 2, 16, 20, 0, 0), ("tiny_transformer", 3, 40, 5, 0, 1),
     ("tiny_gpt", 2, 16, 20, 1, 0), ("tiny_gpt", 2, 16, 20, 0, 0), ("tiny_gpt", 1, 100, 7, 0, 1), ("tiny_gpt", 1, 100, 7, 1, 1),
+    # head size 32 (the smallest the fused attention tile takes; see test_fused_attention_* for the fused runs)
+    ("tiny_attn", 3, 40, 5, 0, 1), ("tiny_attn", 2, 40, 5, 1, 1), ("tiny_attn_causal", 2, 100, 5, 0, 1),
     ("custom", 2, 0, 50, 1, 0), ("custom", 7, 0, 50, 0, 1),
     ("resnet50", 1, 0, 50, 1, 0), ("resnet50", 4, 0, 100, 0, 0), ("resnet50", 4, 0, 100, 0, 1),
     ("bert_base", 1, 128, 20, 1, 0), ("bert_base", 4, 128, 100, 0, 0), ("bert_base", 4, 128, 100, 0, 1),
@@ -464,11 +466,13 @@ def test_residual_fused_into_producer_equals_separate_layer(name, batch, seq, mn
         assert np.array_equal(a, b), f"layer {i + 1} ({types[i]}) differs"
 
 
-@pytest.mark.parametrize("name,batch,seq,mn", [("resnet50", 2, 0, 100), ("tiny_transformer", 3, 24, 20)])
-def test_dropping_pre_add_outputs_changes_no_other_layer(name, batch, seq, mn, workdir):
+@pytest.mark.parametrize("name,batch,seq,mn", [("resnet50", 2, 0, 100), ("tiny_transformer", 3, 24, 20), ("tiny_attn", 2, 64, 5)])
+def test_dropping_pre_add_outputs_changes_no_other_layer(name, batch, seq, mn, workdir, monkeypatch):
     """aspen_b200_set_hidden_states(0): a convolution / matmul whose output only feeds the residual add fused into
     its own epilogue does not write that output.  Every other layer and the result stay bit-identical; the dropped
     layers read as zeros."""
+    if name == "tiny_attn":
+        monkeypatch.setenv("ASPEN_B200_ATTN_FUSE", "1")      # then the attention_k matrices are dropped as well
     cfg, wf = harness.prepare(name, workdir)
     L = api.lib()
     runs = []
@@ -486,12 +490,61 @@ def test_dropping_pre_add_outputs_changes_no_other_layer(name, batch, seq, mn, w
     dropped = [i for i, (a, b) in enumerate(zip(*runs)) if not np.array_equal(a, b)]
     assert dropped, "no layer was dropped"
     for i in dropped:
-        assert types[i] in ("CONV", "MATMUL") and types[i + 1] != "NO_LAYER_TYPE"
+        assert types[i] in ("CONV", "MATMUL", "K_ATTENTION")
         assert not runs[1][i].any(), f"layer {i + 1} differs but is not all zero"
         assert runs[0][i].any()
     assert np.array_equal(runs[0][-1], runs[1][-1])
     n_res = sum(1 for t in types if t == "RESIDUAL")
-    assert n_res - 1 <= len(dropped) <= n_res          # a residual add whose other operand is the network input stays a layer of its own
+    n_conv_like = sum(1 for i in dropped if types[i] != "K_ATTENTION")
+    assert n_res - 1 <= n_conv_like <= n_res          # a residual add whose other operand is the network input stays a layer of its own
+
+
+@pytest.mark.parametrize("name,batch,seq,mn,profile", [("tiny_attn", 3, 40, 5, 1), ("tiny_attn", 2, 128, 5, 1), ("tiny_attn_causal", 2, 100, 5, 1),
+                                                       ("tiny_attn_causal", 3, 24, 5, 0), ("bert_base", 2, 128, 100, 1), ("gpt2_124M", 2, 64, 50, 1)])
+def test_fused_attention_one_key_group_still_writes_the_probabilities(name, batch, seq, mn, profile, workdir, monkeypatch):
+    """ASPEN_B200_ATTN_FUSE=1: attention_k + attention_v run as one tile.  With at most 128 keys the tile also writes the
+    attention_k layer's matrix, so every layer is compared with the oracle as usual."""
+    if not ref.available() and name in ("bert_base", "gpt2_124M"):
+        pytest.skip("needs the reference build")
+    monkeypatch.setenv("ASPEN_B200_ATTN_FUSE", "1")
+    cfg, wf = harness.prepare(name, workdir)
+    dev = harness.Device(cfg, wf, batch, seq, mn, 0, profile)
+    x = harness.make_input(name, dev.input_shape())
+    assert dev.run(x) == 0, api.last_error()
+    outs = oracle_layers(name, cfg, wf, batch, seq, mn, x)
+    check_layers(dev, outs, 0, name)
+    dev.close()
+
+
+@pytest.mark.parametrize("name,batch,seq,mn", [("tiny_attn", 2, 256, 20), ("tiny_attn", 2, 192, 20), ("tiny_attn_causal", 2, 384, 20),
+                                               ("tiny_attn_causal", 1, 512, 20)])
+def test_fused_attention_over_several_key_groups(name, batch, seq, mn, workdir, monkeypatch):
+    """Sequences longer than one group of 128 keys: the fused attention tile accumulates P x V over the groups (and, with a
+    causal mask, skips the groups above its queries).  The probabilities then never reach memory, so this needs
+    aspen_b200_set_hidden_states(0); every layer that is still written is compared with the oracle."""
+    monkeypatch.setenv("ASPEN_B200_ATTN_FUSE", "1")
+    cfg, wf = harness.prepare(name, workdir)
+    L = api.lib()
+    L.aspen_b200_set_hidden_states(0)
+    try:
+        dev = harness.Device(cfg, wf, batch, seq, mn, 0, 1)
+        x = harness.make_input(name, dev.input_shape())
+        assert dev.run(x) == 0, api.last_error()
+    finally:
+        L.aspen_b200_set_hidden_states(1)
+    outs = oracle_layers(name, cfg, wf, batch, seq, mn, x)
+    types = [api.LAYER_TYPES[dev.nasm.ldata_info(i)["type"]] for i in range(dev.nasm.num_ldata)]
+    fused = 0
+    for i in range(1, dev.nasm.num_ldata):
+        got, want = dev.nasm.ldata(i), outs[i]
+        if not got.any():
+            assert types[i] in ("K_ATTENTION", "MATMUL")          # never written: fused away
+            fused += types[i] == "K_ATTENTION"
+            continue
+        err = float(np.abs(got.astype(np.float64) - want).max()) / float(np.abs(want).max())
+        assert err <= TF32_NORM, f"{name} layer {i} ({types[i]}): normalised error {err:.3e}"
+    assert fused == 2                                            # both attention_k layers
+    dev.close()
 
 
 def test_two_graphs_in_flight_upload_and_download_overlap_a_run(workdir):
