@@ -275,7 +275,7 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
                 }
             } else {
                 const unsigned k = issued & 1u;
-                if (lane == 0) { sh->mailbox[k] = next; tc::mbar_arrive(&sh->posted[k]); }
+                if (lane == 0) { sh->tile_desc[k] = T; sh->tile_nasm[k] = g; sh->mailbox[k] = next; tc::mbar_arrive(&sh->posted[k]); }
                 // remember what retiring this tile will need (loaded now, off the critical path)
                 fl_nasm[k] = g; fl_off[k] = T.child_off; fl_cnt[k] = T.child_cnt; fl_layer[k] = T.layer;
                 issued++;
@@ -360,10 +360,8 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
             const unsigned gid = sh->mailbox[k];
             if (gid == ASPEN_TILE_NONE) break;
             if (my_prof && tid == 0) { unsigned long long now = global_ns(); my_prof[PROF_SLOTS - 1] += now - t_mark; t_mark = now; }
-            unsigned g = 0;
-            while (g + 1u < n_nasm && gid >= nasms[g + 1u].tile_base) g++;
-            const NasmDev &G = nasms[g];
-            const TileDev T = G.tiles[gid - G.tile_base];
+            const NasmDev &G = nasms[sh->tile_nasm[k]];
+            const TileDev T = sh->tile_desc[k];
             const LayerDev &L = G.layers[T.layer];
             run_tile<TENSOR_CORES, ATTENTION>(L, T, G, stage_mem, sh, ps, ctrl, status);
             if (my_prof && tid == 0) {

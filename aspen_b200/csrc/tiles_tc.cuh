@@ -55,6 +55,8 @@ struct Shared {
     unsigned long long posted[2];     // scheduler -> executors: mailbox slot holds a tile
     unsigned long long finished[2];   // executors -> scheduler: every executor thread is done with the slot's tile
     unsigned mailbox[2];
+    TileDev tile_desc[2];             // scheduler -> executors: the posted tile's descriptor (the scheduler has loaded it anyway)
+    unsigned tile_nasm[2];            // ... and the index of its graph in the run
     unsigned long long res_full[NW / 32];   // per worker warp: its residual-operand box has landed
     // fused attention tile: queries / a key group / a value group have landed (TMA), the scores of a group are complete
     // (tcgen05.commit), the workers have written the group's probabilities to shared memory, the group's P x V MMAs are complete

@@ -225,6 +225,8 @@ class Net:
         builder, _, self.seq, scheme, wseed, iseed = WORKLOADS[workload]
         self.cfg, self.wfile = prepare_files(workload, workdir)
         q_h, q_w, mn = TILING[workload]
+        if min_ninst and batch <= 8 and self.seq == 0:
+            q_h, min_ninst = 64, 148          # small shards are latency bound: shorter tiles, more of them (measured sweep at batch 4)
         self.tiling = (q_h, q_w, min_ninst or mn)
         self.L.aspen_b200_set_tile_quanta(q_h, q_w, 100000000)
         self.dnn = api.Dnn(self.cfg, self.wfile)
@@ -520,7 +522,7 @@ def extra_legs(args, rank, world, wd, net, workload):
     gb = WORKLOADS[workload][1]
     if world > 1 and gb % world == 0:
         lo, hi = strong_shard(gb, rank, world)
-        s = Net(workload, hi - lo, wd, graphs=1, min_ninst=100)
+        s = Net(workload, hi - lo, wd, graphs=1, min_ninst=100 if hi - lo <= 8 else None)
         rows = net.x.shape[0] // gb
         s.x_pinned.copy_(net.x_pinned[lo * rows:hi * rows])       # this rank's samples of the global batch
         s.warm()
@@ -547,7 +549,7 @@ def extra_legs(args, rank, world, wd, net, workload):
     assign = by_model_assignment(rank, world)
     if assign and assign[1] >= 1:
         name, nb = assign
-        m = Net(name, nb, wd, graphs=1, min_ninst=100 if nb < 16 else None)
+        m = Net(name, nb, wd, graphs=1, min_ninst=100 if nb <= 8 else None)
         m.warm()
         barrier(world, True)
         mms, _ = m.time_blocks(3, steps, 3)
