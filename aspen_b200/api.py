@@ -35,7 +35,7 @@ aspen_b200_last_error aspen_b200_group_status aspen_b200_set_tile_profile aspen_
 aspen_b200_set_precision aspen_b200_set_device aspen_b200_dnn_num_layers aspen_b200_dnn_layer_params
 aspen_b200_dnn_layer_type aspen_b200_nasm_num_ldata aspen_b200_nasm_num_ninst aspen_b200_nasm_total_flops
 aspen_b200_nasm_ldata_info aspen_b200_nasm_ninst_info aspen_b200_nasm_ninst_parents aspen_b200_nasm_ninst_children
-aspen_b200_nasm_get_ldata_packed aspen_b200_group_time_runs aspen_b200_group_profile aspen_b200_generate_nasm aspen_b200_set_hidden_states aspen_b200_dnn_set_embedding
+aspen_b200_nasm_get_ldata_packed aspen_b200_group_time_runs aspen_b200_group_time_passes aspen_b200_dse_group_set_service aspen_b200_group_profile aspen_b200_generate_nasm aspen_b200_set_hidden_states aspen_b200_dnn_set_embedding
 aspen_b200_rpool_add_nasm_tokens aspen_b200_matmul_noalloc""".split()
 
 
@@ -76,6 +76,8 @@ def lib():
         "aspen_b200_nasm_ninst_parents": (u, [vp, u, vp, u]), "aspen_b200_nasm_ninst_children": (u, [vp, u, vp, u]),
         "aspen_b200_nasm_get_ldata_packed": (C.c_long, [vp, u, vp]),
         "aspen_b200_group_time_runs": (C.c_double, [vp, u, u, C.POINTER(C.c_ulonglong)]),
+        "aspen_b200_group_time_passes": (C.c_double, [vp, u, u, C.POINTER(C.c_ulonglong)]),
+        "aspen_b200_dse_group_set_service": (C.c_int, [vp, C.c_int]),
         "aspen_b200_group_profile": (i, [vp, vp, C.POINTER(u)]),
         "aspen_b200_generate_nasm": (vp, [vp, u, u, C.POINTER(u)]),
         "aspen_b200_matmul_noalloc": (i, [vp, vp, vp, vp, u, u, u, i, vp]),
@@ -273,6 +275,18 @@ class DseGroup:
         ms = lib().aspen_b200_group_time_runs(self.h, warmup, iters, C.byref(n))
         if ms < 0:
             raise RuntimeError("timed runs failed: " + last_error())
+        return ms, int(n.value)
+
+    def set_service(self, on: bool) -> None:
+        """Service mode: dse_group_run launches one resident kernel that serves every later rpool add until stop()."""
+        if lib().aspen_b200_dse_group_set_service(self.h, 1 if on else 0) != 0:
+            raise RuntimeError("service mode: " + last_error())
+
+    def time_passes(self, warmup: int, passes: int) -> tuple[float, int]:
+        n = C.c_ulonglong(0)
+        ms = lib().aspen_b200_group_time_passes(self.h, warmup, passes, C.byref(n))
+        if ms < 0:
+            raise RuntimeError("timed passes failed: " + last_error())
         return ms, int(n.value)
 
     def profile(self):

@@ -64,6 +64,24 @@ struct TileDev {
 // producer): the scheduler completes it as soon as it is ready, no executor runs it.
 #define TILE_WRITTEN_BY_PARENTS 1u
 
+// Service mode: the layer-0 tiles run on the device and turn what the host uploaded into the layer's activation
+// matrix, so a graph's next pass can start inside the running kernel.
+struct InputDev {
+    const float *stage;       // packed [column][rows] copy as uploaded; nullptr when the upload goes straight into layer 0
+    const int *ids;           // token ids as uploaded (one per column), nullptr otherwise
+    const float *emb_tok, *emb_pos;
+    unsigned emb_vocab, emb_seq;
+    float *padded;            // zero-padded [sample][PH][PW][4] copy of the image (A_TMA_ROWS), nullptr otherwise
+    unsigned IC, IH, IW, PH, PW, pad;
+    unsigned round;           // values are rounded to TF32 (nearest)
+};
+
+// words of NasmDev::svc
+#define SVC_TARGET 0u         // written by the host: number of the last pass asked for
+#define SVC_STARTED 1u        // number of the last pass started
+#define SVC_IDLE 2u           // 1: no pass in progress
+#define SVC_COUNT 3u          // tiles completed since the kernel was launched
+
 struct NasmDev {
     const LayerDev *layers;
     const TileDev *tiles;
@@ -81,6 +99,12 @@ struct NasmDev {
     unsigned n_tiles, n_layers, n_init, n_input_tiles;   // n_input_tiles: every tile complete when armed (input + bypassed)
     unsigned tile_base;              // global id of local tile 0 in this run
     unsigned queue_base;             // where this graph's initial ready tiles go in the queue
+    // service mode
+    unsigned *svc;                   // SVC_* words in device memory
+    unsigned svc_base;               // passes complete when the kernel was launched
+    unsigned n_exec;                 // tiles that complete in one pass (every tile but the bypassed ones)
+    unsigned n_input;                // layer-0 tiles (local ids 0 .. n_input-1): the seeds of a pass
+    InputDev input;
 };
 
 struct CtrlDev {
@@ -94,6 +118,11 @@ struct CtrlDev {
     unsigned n_nasm;
     unsigned long long stall_ns;   // no-progress window after which a wait gives up
     unsigned long long pipe_ns;    // time budget of in-kernel pipeline waits
+    // service mode
+    unsigned svc_stop;       // host request: leave once no pass is running or asked for
+    unsigned svc_close;      // set by the device: everybody leaves (no error)
+    unsigned busy;           // graphs with a pass in progress
+    unsigned long long idle_ns;    // leave after this long without a pass in progress
 };
 
 struct StatusHost {          // mapped host memory

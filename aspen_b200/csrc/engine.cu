@@ -21,6 +21,13 @@
         }                                                                                       \
     } while (0)
 
+struct Engine;
+static int svc_halt(Engine *e);
+static int svc_run(Engine *e, const std::vector<nasm_t *> &nasms);
+static int svc_wait(nasm_t *nasm);
+static int svc_attach(Engine *e, nasm_t *nasm, const void *input_host, const int *ids_host, bool keep_input);
+static bool svc_done(const struct DeviceNasm *dn);
+
 static thread_local int g_device = -1;
 
 extern "C" int aspen_b200_set_device(int device) {
@@ -191,6 +198,13 @@ struct Engine {
     unsigned long long stall_ns = 2000000000ull;
     unsigned long long pipe_ns = 1000000000ull;
     unsigned long long launches = 0;
+    // service mode: one kernel serves pass after pass of its graphs until dse_group_stop (see scheduler.cuh)
+    bool service = false;             // the group runs its graphs this way
+    bool svc_live = false;            // a service kernel was launched and has not yet been seen to end
+    std::vector<nasm_t *> svc_graphs; // the graphs that kernel serves
+    std::vector<nasm_t *> svc_pool;   // every graph of the group's rpool that has a device image: what the next launch serves
+    unsigned long long idle_ns = 20000000ull;   // the kernel leaves after this long with no pass running
+    cudaEvent_t svc_armed_ev = nullptr;
     float *xfer = nullptr;            // device staging for packed inputs / results
     unsigned long long *prof = nullptr;   // per-CTA time accounting, allocated when ASPEN_B200_PROFILE is set
     size_t xfer_bytes = 0;
@@ -212,6 +226,12 @@ struct DeviceNasm {
     bool armed = false;  // has input, counters will be reset at the next run
     bool round_input = false;   // tensor-core path: the input is rounded to TF32 after upload
     bool ran = false;
+    // service mode
+    unsigned *svc_d = nullptr;                               // SVC_* words
+    unsigned *svc_done_h = nullptr, *svc_done_d = nullptr;   // mapped: number of the last complete pass
+    unsigned svc_armed = 0;                                  // number of the last pass the host has asked for
+    unsigned n_exec = 0, n_input = 0;
+    bool svc_ids = false;                                    // the last input was token ids
     bool fused_attention = false;   // some attention_v layer computes its own probabilities: the run needs the kernel that has that tile
     // Transfers next to a running graph: only DMA goes to the transfer stream (a kernel could not start while the
     // scheduler kernel holds every SM's shared memory); the scatter of a strided input and the gather of the last
@@ -290,6 +310,12 @@ Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) 
         ok = a == cudaSuccess;
         if (ok && precision == 0)
             ok = cudaFuncSetAttribute(sched::scheduler_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes) == cudaSuccess;
+        if (ok)
+            ok = (precision == 0
+                ? cudaFuncSetAttribute(sched::scheduler_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes)
+                : cudaFuncSetAttribute(sched::scheduler_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes)) == cudaSuccess;
+        ok = ok && cudaEventCreateWithFlags(&e->svc_armed_ev, cudaEventDisableTiming) == cudaSuccess;
+        if (env_u64("ASPEN_B200_IDLE_MS", &v) && v > 0) e->idle_ns = v * 1000000ull;
     }
     if (ok && getenv("ASPEN_B200_PROFILE")) {
         size_t bytes = (size_t)e->n_ctas * sched::PROF_SLOTS * sizeof(unsigned long long);
@@ -307,10 +333,12 @@ Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) 
 void engine_destroy(Engine *e) {
     if (!e) return;
     cudaSetDevice(e->device);
+    svc_halt(e);
     if (e->stream) cudaStreamSynchronize(e->stream);
     if (e->stream) cudaStreamDestroy(e->stream);
     if (e->side) cudaStreamDestroy(e->side);
     if (e->io) cudaStreamDestroy(e->io);
+    if (e->svc_armed_ev) cudaEventDestroy(e->svc_armed_ev);
     cudaFree(e->ctrl);
     if (e->status_h) cudaFreeHost((void *)e->status_h);
     cudaFree(e->queue);
@@ -335,6 +363,7 @@ static int to_device(T **dst, const std::vector<T> &src) {
 // another graph is running; only a graph that is itself still being computed makes the transfer wait for
 // that run.
 static cudaStream_t io_stream(Engine *e, const nasm_t *nasm) {
+    if (e->service) return e->io;
     if (e->running && std::find(e->in_flight.begin(), e->in_flight.end(), nasm) != e->in_flight.end() &&
         *(volatile unsigned *)nasm->dev->completed_h == 0)
         cudaStreamSynchronize(e->stream);
@@ -456,6 +485,8 @@ static void free_device_nasm(DeviceNasm *dn) {
     cudaFree(dn->dep_init); cudaFree(dn->layer_done); cudaFree(dn->layer_tiles); cudaFree(dn->init_ready);
     cudaFree(dn->layers_completed); cudaFree(dn->layer_done_init); cudaFree(dn->wmaps);
     if (dn->completed_h) cudaFreeHost(dn->completed_h);
+    if (dn->svc_done_h) cudaFreeHost(dn->svc_done_h);
+    cudaFree(dn->svc_d);
     cudaFree(dn->in_stage); cudaFree(dn->ids_stage); cudaFree(dn->res_packed); cudaFree(dn->padded_in);
     for (float *p : dn->scratch) cudaFree(p);
     if (dn->in_consumed) cudaEventDestroy(dn->in_consumed);
@@ -851,6 +882,13 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
     CUDA_TRY(cudaHostAlloc(&dn->completed_h, sizeof(unsigned), cudaHostAllocMapped));
     *dn->completed_h = 0;
     CUDA_TRY(cudaHostGetDevicePointer(&dn->completed_d, dn->completed_h, 0));
+    CUDA_TRY(cudaHostAlloc(&dn->svc_done_h, sizeof(unsigned), cudaHostAllocMapped));
+    *dn->svc_done_h = 0;
+    CUDA_TRY(cudaHostGetDevicePointer(&dn->svc_done_d, dn->svc_done_h, 0));
+    CUDA_TRY(cudaMalloc(&dn->svc_d, 4 * sizeof(unsigned)));
+    CUDA_TRY(cudaMemset(dn->svc_d, 0, 4 * sizeof(unsigned)));
+    dn->n_exec = n - n_bypassed;
+    dn->n_input = n_input;
 
     {
         const nasm_ldata_t &l0 = nasm->ldata[0], &ll = nasm->ldata[nasm->num_ldata - 1];
@@ -917,6 +955,12 @@ int engine_set_input(nasm_t *nasm, const void *input_host) {
     return 0;
 }
 
+bool engine_in_service(Engine *e) { return e && e->service; }
+int engine_service_tokens(Engine *e, nasm_t *nasm, const int *ids_host) {
+    if (!e || !e->service || !ids_host) return -1;
+    return svc_attach(e, nasm, nullptr, ids_host, false);
+}
+
 int engine_set_tokens(nasm_t *nasm, const int *ids_host) {
     DeviceNasm *dn = nasm->dev;
     if (!dn || !ids_host) return -1;
@@ -960,6 +1004,7 @@ int engine_set_tokens(nasm_t *nasm, const int *ids_host) {
 
 int engine_attach_nasm(Engine *e, nasm_t *nasm, const void *input_host) {
     if (!e) return -1;
+    if (e->service) return svc_attach(e, nasm, input_host, nullptr, false);
     CUDA_TRY(cudaSetDevice(e->device));
     if (nasm->dev && nasm->dev->e != e) { engine_detach_nasm(nasm); }
     if (!nasm->dev) {
@@ -977,6 +1022,8 @@ void engine_detach_nasm(nasm_t *nasm) {
     if (!dn) return;
     Engine *e = dn->e;
     cudaSetDevice(e->device);
+    svc_halt(e);
+    e->svc_pool.erase(std::remove(e->svc_pool.begin(), e->svc_pool.end(), nasm), e->svc_pool.end());
     if (e->running) { cudaStreamSynchronize(e->stream); e->running = false; }
     e->in_flight.erase(std::remove(e->in_flight.begin(), e->in_flight.end(), nasm), e->in_flight.end());
     e->uploaded.clear();
@@ -986,6 +1033,7 @@ void engine_detach_nasm(nasm_t *nasm) {
 
 int engine_rearm(Engine *e, nasm_t *nasm) {
     if (!nasm->dev) return -1;
+    if (e->service) return svc_attach(e, nasm, nullptr, nullptr, true);
     if (e->running && std::find(e->in_flight.begin(), e->in_flight.end(), nasm) != e->in_flight.end()) {
         // re-arming a graph the device is still draining: let that run finish first
         cudaSetDevice(e->device);
@@ -1067,6 +1115,7 @@ static int launch_run(Engine *e, const std::vector<nasm_t *> &run) {
 int engine_run(Engine *e, const std::vector<nasm_t *> &nasms) {
     if (!e) return -1;
     CUDA_TRY(cudaSetDevice(e->device));
+    if (e->service) return svc_run(e, nasms);
     std::vector<nasm_t *> run;
     for (nasm_t *n : nasms)
         if (n->dev && n->dev->e == e && n->dev->armed) run.push_back(n);
@@ -1084,6 +1133,7 @@ int engine_run(Engine *e, const std::vector<nasm_t *> &nasms) {
 }
 
 int engine_stop(Engine *e) {
+    if (e && e->service) { CUDA_TRY(cudaSetDevice(e->device)); return svc_halt(e); }
     if (!e || !e->running) return 0;
     CUDA_TRY(cudaSetDevice(e->device));
     if (cudaStreamQuery(e->stream) == cudaErrorNotReady) {
@@ -1103,13 +1153,17 @@ int engine_stop(Engine *e) {
     return 0;
 }
 
-unsigned int engine_poll_nasm(nasm_t *nasm) { return nasm->dev ? *(volatile unsigned *)nasm->dev->completed_h : 0; }
+unsigned int engine_poll_nasm(nasm_t *nasm) {
+    if (nasm->dev && nasm->dev->e->service) return svc_done(nasm->dev) ? 1u : 0u;
+    return nasm->dev ? *(volatile unsigned *)nasm->dev->completed_h : 0;
+}
 
 int engine_wait_nasm(nasm_t *nasm) {
     DeviceNasm *dn = nasm->dev;
     if (!dn) return -1;
     Engine *e = dn->e;
     cudaSetDevice(e->device);
+    if (e->service) return svc_wait(nasm);
     for (unsigned spin = 0;; spin++) {
         if (*(volatile unsigned *)dn->completed_h) return 0;
         if (!e->running) return -1;
@@ -1128,6 +1182,16 @@ long engine_read_ldata(nasm_t *nasm, unsigned int idx, float *out) {
     const nasm_ldata_t &ld = nasm->ldata[idx];
     const size_t n = (size_t)ld.out_mat_dims[OUT_H] * ld.out_mat_dims[OUT_W];
     const float *src = (const float *)((char *)dn->arena + dn->ldata_off[idx]);
+    if (e->service && e->svc_live) {
+        // a kernel could not start next to the resident one: strided matrices are packed by the copy engine
+        const size_t row = (size_t)ld.out_mat_dims[OUT_H] * sizeof(float);
+        if (cudaMemcpy2DAsync(out, row, src, (size_t)ld.out_mat_stride * sizeof(float), row, ld.out_mat_dims[OUT_W], cudaMemcpyDeviceToHost, e->io) != cudaSuccess ||
+            cudaStreamSynchronize(e->io) != cudaSuccess) {
+            ASPEN_ERR("CUDA error reading layer %u: %s\n", idx, cudaGetErrorString(cudaGetLastError()));
+            return -1;
+        }
+        return (long)n;
+    }
     if (idx == nasm->num_ldata - 1 && dn->res_valid) {
         // the last layer of a graph that has run: already gathered (or packed by layout); DMA only
         if (cudaStreamWaitEvent(e->io, dn->res_ready, 0) != cudaSuccess) return -1;
@@ -1159,6 +1223,7 @@ double engine_time_runs(Engine *e, const std::vector<nasm_t *> &nasms, unsigned 
     for (nasm_t *n : nasms)
         if (n->dev && n->dev->e == e) run.push_back(n);
     if (run.empty()) return -1.0;
+    if (svc_halt(e) != 0) return -1.0;
     if (e->running) { cudaStreamSynchronize(e->stream); e->running = false; e->in_flight.clear(); }
     for (unsigned i = 0; i < warmup + iters; i++) {
         if (i == warmup) { cudaEventRecord(t0, e->stream); l0 = e->launches; }
@@ -1181,12 +1246,261 @@ double engine_time_runs(Engine *e, const std::vector<nasm_t *> &nasms, unsigned 
     return (double)ms;
 }
 
+// ---- service mode ---------------------------------------------------------------------------------------------------
+// Host side of the resident kernel described in scheduler.cuh.  dse_group_run launches it over every graph of the pool;
+// rpool_add_nasm* on a graph it serves uploads the input on the transfer stream and then writes the graph's pass number
+// to the device with a 4-byte copy on the same stream; dse_wait_for_nasm_completion polls the graph's mapped word;
+// dse_group_stop asks the kernel to leave and waits for it.  The kernel also leaves by itself (idle, or the queue of
+// the launch used up); whoever next runs or waits launches it again when passes are still owed, and a pass cut short
+// simply starts over (a pass only reads its input and writes its own matrices).
+// Nothing that allocates or frees device memory, and no kernel, may be issued while the kernel is resident: those paths
+// stop it first.
+static bool svc_done(const DeviceNasm *dn) { return *(volatile unsigned *)dn->svc_done_h == dn->svc_armed; }
+
+static int svc_halt(Engine *e) {
+    if (!e->svc_live) return 0;
+    if (cudaStreamQuery(e->stream) == cudaErrorNotReady) {
+        unsigned one = 1;
+        cudaMemcpyAsync(&e->ctrl->svc_stop, &one, sizeof(unsigned), cudaMemcpyHostToDevice, e->side);
+    }
+    cudaError_t err = cudaStreamSynchronize(e->stream);
+    cudaStreamSynchronize(e->side);
+    cudaStreamSynchronize(e->io);
+    e->svc_live = false;
+    e->svc_graphs.clear();
+    if (err != cudaSuccess) { ASPEN_ERR("CUDA error after a service run: %s\n", cudaGetErrorString(err)); e->status_h->status = ASPEN_B200_ERR_CUDA; return -1; }
+    return 0;
+}
+
+static int svc_launch(Engine *e, const std::vector<nasm_t *> &graphs, unsigned stop_when_done) {
+    std::vector<NasmDev> images(graphs.size());
+    unsigned total = 0;
+    for (size_t i = 0; i < graphs.size(); i++) {
+        nasm_t *nasm = graphs[i];
+        DeviceNasm *dn = nasm->dev;
+        if (dn->fused_attention) { ASPEN_ERR("service mode: graphs with the fused attention tile are run per launch only\n"); return -1; }
+        NasmDev &G = images[i];
+        G = dn->host;
+        G.tile_base = total;
+        total += G.n_tiles;
+        G.svc = dn->svc_d; G.svc_base = *(volatile unsigned *)dn->svc_done_h; G.completed = dn->svc_done_d;
+        G.n_exec = dn->n_exec; G.n_input = dn->n_input;
+        InputDev &I = G.input;
+        memset(&I, 0, sizeof I);
+        I.round = dn->round_input ? 1u : 0u;
+        if (dn->svc_ids) {
+            I.ids = dn->ids_stage; I.emb_tok = dn->dd->emb_token; I.emb_pos = dn->dd->emb_position;
+            I.emb_vocab = nasm->dnn->emb_vocab; I.emb_seq = nasm->tr_seq_len ? nasm->tr_seq_len : 1u;
+        } else I.stage = dn->in_stage;
+        I.padded = dn->padded_in; I.IC = dn->pin_ic; I.IH = dn->pin_ih; I.IW = dn->pin_iw; I.PH = dn->pin_ph; I.PW = dn->pin_pw; I.pad = dn->pin_pad;
+    }
+    if (total >= (1u << 30)) { ASPEN_ERR("service mode: too many tiles\n"); return -1; }
+    // queue of the launch: room for a number of passes; when it is used up the kernel leaves and is launched again
+    const unsigned passes = std::max(4u, std::min(256u, (8u << 20) / std::max(total, 1u)));
+    const unsigned cap = total * passes;
+    if (graphs.size() > e->nasms_cap) {
+        cudaFree(e->nasms_d);
+        e->nasms_d = nullptr;
+        e->nasms_cap = 0;
+        CUDA_TRY(cudaMalloc(&e->nasms_d, graphs.size() * sizeof(NasmDev)));
+        e->nasms_cap = (unsigned)graphs.size();
+    }
+    if (cap > e->queue_cap) {
+        cudaFree(e->queue);
+        e->queue = nullptr;
+        e->queue_cap = 0;
+        CUDA_TRY(cudaMalloc(&e->queue, (size_t)cap * sizeof(unsigned)));
+        e->queue_cap = cap;
+    }
+    e->uploaded.clear();     // the per-launch path must upload its own images again
+    CUDA_TRY(cudaMemcpyAsync(e->nasms_d, images.data(), images.size() * sizeof(NasmDev), cudaMemcpyHostToDevice, e->stream));
+    unsigned n_nasm = (unsigned)graphs.size();
+    CUDA_TRY(cudaMemcpyAsync(&e->ctrl->n_nasm, &n_nasm, sizeof(unsigned), cudaMemcpyHostToDevice, e->stream));
+    for (nasm_t *nasm : graphs)
+        CUDA_TRY(cudaMemcpyAsync(&nasm->dev->svc_d[SVC_TARGET], &nasm->dev->svc_armed, sizeof(unsigned), cudaMemcpyHostToDevice, e->stream));
+    // pass numbers written later (transfer stream) must not be overtaken by the ones above
+    CUDA_TRY(cudaEventRecord(e->svc_armed_ev, e->stream));
+    CUDA_TRY(cudaStreamWaitEvent(e->io, e->svc_armed_ev, 0));
+    e->status_h->status = 0;
+    e->status_h->tiles_done = 0;
+    sched::svc_arm_kernel<<<std::min<unsigned>((cap + 255) / 256, 2048), 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue, cap, total, e->stall_ns, e->pipe_ns,
+                                                                                               e->idle_ns, stop_when_done);
+    if (e->precision == 0)
+        sched::scheduler_kernel<true, false, true><<<e->n_ctas, sched::SCHED_THREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
+    else
+        sched::scheduler_kernel<false, false, true><<<e->n_ctas, sched::SCHED_THREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
+    e->launches += 2;
+    CUDA_TRY(cudaGetLastError());
+    e->svc_graphs = graphs;
+    e->svc_live = true;
+    for (nasm_t *nasm : graphs) { nasm->dev->ran = true; nasm->dev->res_valid = false; }
+    return 0;
+}
+
+static void svc_pool_add(Engine *e, const std::vector<nasm_t *> &nasms) {
+    for (nasm_t *n : nasms)
+        if (n->dev && n->dev->e == e && std::find(e->svc_pool.begin(), e->svc_pool.end(), n) == e->svc_pool.end()) e->svc_pool.push_back(n);
+}
+static bool svc_serves(Engine *e, const nasm_t *nasm) {
+    return e->svc_live && std::find(e->svc_graphs.begin(), e->svc_graphs.end(), nasm) != e->svc_graphs.end();
+}
+
+// dse_group_run in service mode.
+static int svc_run(Engine *e, const std::vector<nasm_t *> &nasms) {
+    svc_pool_add(e, nasms);
+    const std::vector<nasm_t *> graphs = e->svc_pool;
+    if (graphs.empty()) return 0;
+    if (e->svc_live) {
+        bool served = cudaStreamQuery(e->stream) == cudaErrorNotReady;
+        for (nasm_t *n : graphs) served = served && svc_serves(e, n);
+        if (served) return 0;         // the passes asked for since were signalled to the resident kernel
+        if (svc_halt(e) != 0) return -1;
+    }
+    bool owed = false;
+    for (nasm_t *n : graphs) owed = owed || !svc_done(n->dev);
+    return owed ? svc_launch(e, graphs, 0u) : 0;
+}
+
+// dse_wait_for_nasm_completion in service mode.
+static int svc_wait(nasm_t *nasm) {
+    DeviceNasm *dn = nasm->dev;
+    Engine *e = dn->e;
+    unsigned relaunches = 0;
+    for (unsigned spin = 0;; spin++) {
+        if (svc_done(dn)) return 0;
+        if (e->status_h->status != 0) return -1;
+        cudaError_t q = svc_serves(e, nasm) ? cudaStreamQuery(e->stream) : cudaSuccess;
+        if (q == cudaSuccess) {
+            // no kernel serves the graph (never launched for it; or it left: idle, queue used up, a request that just
+            // missed it): launch for everything that is owed.  Every launch completes at least the pass it was launched
+            // for unless it reports an error, so a few launches in a row without this graph completing is a fault.
+            if (svc_done(dn)) return 0;
+            if (e->status_h->status != 0 || ++relaunches > 1000u) { ASPEN_ERR("service mode: the graph's pass does not complete\n"); return -1; }
+            if (svc_halt(e) != 0 || svc_launch(e, e->svc_pool, 0u) != 0) return -1;
+        } else if (q != cudaErrorNotReady) {
+            ASPEN_ERR("CUDA error while waiting: %s\n", cudaGetErrorString(q));
+            e->status_h->status = ASPEN_B200_ERR_CUDA;
+            return -1;
+        }
+        if (spin > 64) sched_yield();
+    }
+}
+
+// rpool_add_nasm* in service mode: upload (input_host, or ids_host, or neither = keep what layer 0 / the staging copy
+// holds) and ask for one more pass of the graph.
+static int svc_attach(Engine *e, nasm_t *nasm, const void *input_host, const int *ids_host, bool keep_input) {
+    CUDA_TRY(cudaSetDevice(e->device));
+    if (nasm->dev && nasm->dev->e != e) { if (svc_halt(e) != 0) return -1; engine_detach_nasm(nasm); }
+    if (!nasm->dev) {
+        if (svc_halt(e) != 0) return -1;
+        if (build_device_nasm(e, nasm) != 0) { engine_detach_nasm(nasm); return -1; }
+        CUDA_TRY(cudaStreamSynchronize(e->stream));
+    }
+    DeviceNasm *dn = nasm->dev;
+    svc_pool_add(e, std::vector<nasm_t *>{nasm});
+    // the previous pass of this graph is still owed: its input must stay until that pass is complete
+    if (!svc_done(dn) && svc_wait(nasm) != 0) return -1;
+    const nasm_ldata_t &l0 = nasm->ldata[0];
+    const size_t n = (size_t)l0.out_mat_dims[OUT_H] * l0.out_mat_dims[OUT_W];
+    float *dst = (float *)((char *)dn->arena + dn->ldata_off[0]);
+    if (ids_host) {
+        aspen_dnn_t *dnn = nasm->dnn;
+        const unsigned M = l0.out_mat_dims[OUT_H];
+        if (dnn->emb_token.empty() || dnn->emb_width != M || M % 4 != 0 || l0.out_mat_stride % 4 != 0 || l0.ninst_tile_dims[OUT_H] % 4 != 0) {
+            ASPEN_ERR("token input: the dnn has no embedding table of width %u (aspen_b200_dnn_set_embedding), or the width is not a multiple of 4\n", M);
+            return -1;
+        }
+        if (!dnn->emb_position.empty() && nasm->tr_seq_len > dnn->emb_max_pos) { ASPEN_ERR("token input: sequence length %u exceeds the position table (%u rows)\n", nasm->tr_seq_len, dnn->emb_max_pos); return -1; }
+        DeviceDnn *dd = dn->dd;
+        if (!dd->emb_token || !dn->ids_stage || !dn->svc_ids) {
+            if (svc_halt(e) != 0) return -1;          // allocations, and the graph's image changes
+            if (!dd->emb_token) {
+                CUDA_TRY(cudaMalloc(&dd->emb_token, dnn->emb_token.size() * sizeof(float)));
+                CUDA_TRY(cudaMemcpy(dd->emb_token, dnn->emb_token.data(), dnn->emb_token.size() * sizeof(float), cudaMemcpyHostToDevice));
+                if (!dnn->emb_position.empty()) {
+                    CUDA_TRY(cudaMalloc(&dd->emb_position, dnn->emb_position.size() * sizeof(float)));
+                    CUDA_TRY(cudaMemcpy(dd->emb_position, dnn->emb_position.data(), dnn->emb_position.size() * sizeof(float), cudaMemcpyHostToDevice));
+                }
+            }
+            if (!dn->ids_stage) CUDA_TRY(cudaMalloc(&dn->ids_stage, (size_t)l0.out_mat_dims[OUT_W] * sizeof(int)));
+            dn->svc_ids = true;
+        }
+        CUDA_TRY(cudaMemcpyAsync(dn->ids_stage, ids_host, (size_t)l0.out_mat_dims[OUT_W] * sizeof(int), cudaMemcpyHostToDevice, e->io));
+        CUDA_TRY(cudaStreamSynchronize(e->io));       // the caller may reuse its buffer as soon as we return
+    } else if (!keep_input) {
+        if (dn->svc_ids) { if (svc_halt(e) != 0) return -1; dn->svc_ids = false; }
+        if (!input_host) {
+            // no input: the staging copy (or layer 0) is cleared; a memset may be a kernel, so the resident kernel leaves first
+            if (svc_halt(e) != 0) return -1;
+            CUDA_TRY(cudaMemsetAsync(dn->in_stage ? dn->in_stage : dst, 0, dn->in_stage ? n * sizeof(float) : l0.out_mat_mem_size, e->stream));
+            CUDA_TRY(cudaStreamSynchronize(e->stream));
+        } else {
+            CUDA_TRY(cudaMemcpyAsync(dn->in_stage ? dn->in_stage : dst, input_host, n * sizeof(float), cudaMemcpyHostToDevice, e->io));
+            CUDA_TRY(cudaStreamSynchronize(e->io));
+        }
+    }
+    dn->svc_armed++;
+    dn->res_valid = false;
+    if (svc_serves(e, nasm))
+        CUDA_TRY(cudaMemcpyAsync(&dn->svc_d[SVC_TARGET], &dn->svc_armed, sizeof(unsigned), cudaMemcpyHostToDevice, e->io));
+    return 0;
+}
+
+int engine_set_service(Engine *e, int on) {
+    if (!e) return -1;
+    CUDA_TRY(cudaSetDevice(e->device));
+    if (e->service == (on != 0)) return 0;
+    if (e->service) { if (svc_halt(e) != 0) return -1; }
+    else if (e->running) { cudaStreamSynchronize(e->stream); e->running = false; e->in_flight.clear(); }
+    e->service = on != 0;
+    return 0;
+}
+
+// `passes` passes, dealt round robin to the pool's graphs, inside service launches that leave when they are done;
+// device time between CUDA events on the compute stream.  Inputs are whatever the graphs hold (layer 0 / staging copy).
+double engine_time_passes(Engine *e, const std::vector<nasm_t *> &nasms, unsigned int warmup, unsigned int passes, unsigned long long *launches) {
+    if (!e || !e->service) return -1.0;
+    if (cudaSetDevice(e->device) != cudaSuccess || svc_halt(e) != 0) return -1.0;
+    svc_pool_add(e, nasms);
+    const std::vector<nasm_t *> graphs = e->svc_pool;
+    if (graphs.empty()) return -1.0;
+    cudaEvent_t t0, t1;
+    if (cudaEventCreate(&t0) != cudaSuccess || cudaEventCreate(&t1) != cudaSuccess) return -1.0;
+    float ms = 0.f;
+    unsigned long long l0 = 0;
+    for (int phase = 0; phase < 2; phase++) {
+        const unsigned count = phase == 0 ? warmup : passes;
+        if (count == 0) continue;
+        for (size_t i = 0; i < graphs.size(); i++)
+            graphs[i]->dev->svc_armed += count / (unsigned)graphs.size() + (i < count % graphs.size() ? 1u : 0u);
+        if (phase == 1) { cudaEventRecord(t0, e->stream); l0 = e->launches; }
+        for (unsigned tries = 0;; tries++) {
+            if (svc_launch(e, graphs, 1u) != 0) return -1.0;
+            if (phase == 1) cudaEventRecord(t1, e->stream);
+            if (svc_halt(e) != 0 || e->status_h->status != 0) {
+                ASPEN_ERR("timed passes failed: engine status %u (info %u %u)\n", e->status_h->status, e->status_h->info0, e->status_h->info1);
+                return -1.0;
+            }
+            bool done = true;
+            for (nasm_t *n : graphs) done = done && svc_done(n->dev);
+            if (done) break;
+            if (tries > 100000u) return -1.0;      // each launch completes at least one pass or reports a stall
+        }
+    }
+    cudaEventElapsedTime(&ms, t0, t1);
+    cudaEventDestroy(t0);
+    cudaEventDestroy(t1);
+    if (launches) *launches = e->launches - l0;
+    return (double)ms;
+}
+
 void engine_flush() {}
 
 // Sums the per-CTA time accounting (ASPEN_B200_PROFILE=1) into out[PROF_SLOTS] and clears it.
 int engine_read_profile(Engine *e, unsigned long long *out, unsigned *n_ctas) {
     if (!e || !e->prof) return -1;
     CUDA_TRY(cudaSetDevice(e->device));
+    if (svc_halt(e) != 0) return -1;
     CUDA_TRY(cudaStreamSynchronize(e->stream));
     std::vector<unsigned long long> h((size_t)e->n_ctas * sched::PROF_SLOTS);
     CUDA_TRY(cudaMemcpy(h.data(), e->prof, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));

@@ -177,6 +177,10 @@ void engine_detach_nasm(nasm_t *nasm);
 int engine_set_input(nasm_t *nasm, const void *input_host);
 int engine_set_tokens(nasm_t *nasm, const int *token_ids_host);   // layer 0 = embedding rows of the ids, gathered on the device
 int engine_rearm(Engine *e, nasm_t *nasm);
+int engine_set_service(Engine *e, int on);                       // service mode: one resident kernel serves pass after pass
+bool engine_in_service(Engine *e);
+int engine_service_tokens(Engine *e, nasm_t *nasm, const int *token_ids_host);
+double engine_time_passes(Engine *e, const std::vector<nasm_t *> &nasms, unsigned int warmup, unsigned int passes, unsigned long long *launches);
 int engine_run(Engine *e, const std::vector<nasm_t *> &nasms);
 int engine_stop(Engine *e);
 int engine_wait_nasm(nasm_t *nasm);

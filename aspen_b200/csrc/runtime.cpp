@@ -75,6 +75,17 @@ extern "C" int aspen_b200_dnn_set_embedding(aspen_dnn_t *dnn, const float *token
 extern "C" void aspen_b200_rpool_add_nasm_tokens(rpool_t *rpool, nasm_t *nasm, const int *token_ids) {
     if (!rpool || !nasm || !token_ids) { ASPEN_ERR("ERROR: aspen_b200_rpool_add_nasm_tokens: NULL argument.\n"); return; }
     if (!rpool->engine) { ASPEN_ERR("ERROR: aspen_b200_rpool_add_nasm_tokens: attach the rpool to a dse group first (the gather runs on its device).\n"); return; }
+    if (engine_in_service(rpool->engine)) {
+        if (!nasm->has_graph) { ASPEN_ERR("ERROR: aspen_b200_rpool_add_nasm_tokens: nasm has no dependency graph.\n"); return; }
+        if (nasm->rpool && nasm->rpool != rpool) { ASPEN_ERR("ERROR: aspen_b200_rpool_add_nasm_tokens: nasm already belongs to another rpool.\n"); return; }
+        bool present = false;
+        for (nasm_t *n : rpool->nasms) present |= n == nasm;
+        if (!present) rpool->nasms.push_back(nasm);
+        nasm->rpool = rpool;
+        nasm->completed.store(0);
+        if (engine_service_tokens(rpool->engine, nasm, token_ids) != 0) ASPEN_ERR("ERROR: aspen_b200_rpool_add_nasm_tokens: device upload failed.\n");
+        return;
+    }
     // the graph joins the pool exactly as with a raw input (image built on first use); layer 0 is then filled from the ids
     if (!nasm->dev || nasm->rpool != rpool) {
         rpool_add_nasm_raw_input(rpool, nasm, nullptr);
@@ -203,6 +214,16 @@ extern "C" void dse_group_run_until_nasm_completion(dse_group_t *g, nasm_t *nasm
     dse_group_run(g);
     dse_wait_for_nasm_completion(nasm);
     dse_group_stop(g);
+}
+
+extern "C" int aspen_b200_dse_group_set_service(dse_group_t *g, int on) {
+    if (!g) { ASPEN_ERR("ERROR: aspen_b200_dse_group_set_service: dse_group is NULL\n"); return -1; }
+    return engine_set_service(g->engine, on);
+}
+
+extern "C" double aspen_b200_group_time_passes(dse_group_t *g, unsigned int warmup, unsigned int passes, unsigned long long *launches) {
+    if (!g || !g->rpool) return -1.0;
+    return engine_time_passes(g->engine, g->rpool->nasms, warmup, passes, launches);
 }
 
 extern "C" int aspen_b200_group_status(dse_group_t *g) { return g ? engine_status(g->engine) : ASPEN_B200_ERR_CUDA; }

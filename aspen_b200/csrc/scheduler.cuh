@@ -48,6 +48,9 @@ __device__ __forceinline__ unsigned ld_relaxed(const unsigned *p) {
 // Child update of a completed tile; called by the whole (converged) scheduler warp.  `children` holds
 // (child tile, count the child waits for) pairs so one load feeds both the atomic and the test.
 // Returns the global id of a child this CTA should run next (only when want_keep), or ASPEN_TILE_NONE.
+// SERVICE: the counters are never reset between the passes of a graph; a pass only starts when the previous one is complete,
+// so a child is ready whenever its counter reaches a multiple of the count it waits for.
+template <bool SERVICE>
 static __device__ unsigned complete_children(const NasmDev &G, unsigned child_off, unsigned child_cnt, CtrlDev *ctrl, unsigned *queue, bool want_keep) {
     const unsigned lane = threadIdx.x & 31u;
     const uint2 *edges = reinterpret_cast<const uint2 *>(G.children);
@@ -60,7 +63,8 @@ static __device__ unsigned complete_children(const NasmDev &G, unsigned child_of
         if (idx < child_cnt) {
             const uint2 e = edges[child_off + idx];
             child = e.x;
-            ready = atomicAdd(&G.dep[child], 1u) + 1u == e.y;
+            const unsigned now = atomicAdd(&G.dep[child], 1u) + 1u;
+            ready = SERVICE ? (now % e.y == 0u) : (now == e.y);
         }
         unsigned mask = __ballot_sync(0xffffffffu, ready);
         if (mask == 0u) continue;
@@ -102,6 +106,97 @@ static __device__ void complete_accounting(const NasmDev &G, unsigned layer, Ctr
     if (((t + 1u) & 1023u) == 0u || t + 1u == ctrl->total) status->tiles_done = t + 1u;
 }
 
+// ---- service mode ------------------------------------------------------------------------------
+// The kernel stays resident while the host keeps asking for passes of the graphs it was launched with (the counterpart
+// of the reference's DSE threads, which run from dse_group_run to dse_group_stop and serve whatever rpool_add_nasm
+// brings, ref src/dse.c:20-108, 215-232).  The host asks for pass number p of a graph by writing p to the graph's
+// SVC_TARGET word (a 4-byte copy that follows the input upload on the transfer stream).  An idle scheduler warp that
+// finds an idle graph with target != started claims it (CAS on SVC_IDLE) and pushes its layer-0 tiles; those tiles
+// prepare the input, everything else follows from the dependency counters.  The warp that retires the last tile of a
+// pass writes the pass number to the graph's mapped host word and marks the graph idle.  The kernel leaves -- without
+// error -- when no pass is running or asked for and the host has asked it to stop, when nothing has run for idle_ns,
+// or when the queue of this launch is used up; the host launches it again if work is left.
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Looks at every graph; starts the next pass where one is asked for.  Whole (converged) warp.
+// Returns bit 0: some graph has a pass in progress, bit 1: a pass is asked for but this launch's queue has no room left,
+// bit 2: this warp started a pass.
+static __device__ unsigned svc_scan(const NasmDev *nasms, unsigned n_nasm, CtrlDev *ctrl, unsigned *queue) {
+    const unsigned lane = threadIdx.x & 31u;
+    unsigned st = 0;
+    for (unsigned g = 0; g < n_nasm; g++) {
+        const NasmDev &G = nasms[g];
+        unsigned go = 0;
+        if (lane == 0) {
+            if (ld_acquire(&G.svc[SVC_IDLE]) == 0u) go = 1u;
+            else if (ld_acquire_sys(&G.svc[SVC_TARGET]) != ld_relaxed(&G.svc[SVC_STARTED])) {
+                if (ld_relaxed(&ctrl->tail) + ctrl->total > ctrl->cap) go = 2u;
+                else if (atomicCAS(&G.svc[SVC_IDLE], 1u, 0u) == 1u) {
+                    // only the holder of the claim changes SVC_STARTED: look again now that it is ours
+                    const unsigned started = ld_relaxed(&G.svc[SVC_STARTED]);
+                    if (ld_acquire_sys(&G.svc[SVC_TARGET]) != started) {
+                        asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(&G.svc[SVC_STARTED]), "r"(started + 1u) : "memory");
+                        atomicAdd(&ctrl->busy, 1u);
+                        go = 4u;
+                    } else asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(&G.svc[SVC_IDLE]), "r"(1u) : "memory");
+                } else go = 1u;
+            }
+        }
+        go = __shfl_sync(0xffffffffu, go, 0);
+        st |= go;
+        if (go == 4u) {
+            unsigned pos = 0;
+            if (lane == 0) pos = atomicAdd(&ctrl->tail, G.n_input);
+            pos = __shfl_sync(0xffffffffu, pos, 0);
+            for (unsigned i = lane; i < G.n_input; i += 32u)
+                if (pos + i < ctrl->cap)
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(&queue[pos + i]), "r"(i + G.tile_base + 1u) : "memory");
+        }
+    }
+    return st;
+}
+
+// Completion accounting in service mode: one counter per graph; every n_exec-th completion ends a pass.
+static __device__ void svc_account(const NasmDev *nasms, unsigned n_nasm, unsigned g, CtrlDev *ctrl, unsigned *queue) {
+    const NasmDev &G = nasms[g];
+    const unsigned lane = threadIdx.x & 31u;
+    unsigned t = 0;
+    if (lane == 0) { atomicAdd(&ctrl->done, 1u); t = atomicAdd(&G.svc[SVC_COUNT], 1u) + 1u; }
+    t = __shfl_sync(0xffffffffu, t, 0);
+    if (t % G.n_exec != 0u) return;
+    if (lane == 0) {
+        __threadfence_system();
+        *G.completed = G.svc_base + t / G.n_exec;          // mapped host word: number of the pass that is complete
+        __threadfence_system();
+        atomicSub(&ctrl->busy, 1u);
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(&G.svc[SVC_IDLE]), "r"(1u) : "memory");
+    }
+    __syncwarp();
+    svc_scan(nasms, n_nasm, ctrl, queue);                  // the next pass of this graph may already be asked for
+}
+
+// Arms a service launch: empty queue, zero counters, every graph idle at the pass count the host has seen complete.
+static __global__ void svc_arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, unsigned cap, unsigned total, unsigned long long stall_ns,
+                               unsigned long long pipe_ns, unsigned long long idle_ns, unsigned svc_stop) {
+    const unsigned stride = gridDim.x * blockDim.x, t0 = blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned n_nasm = ctrl->n_nasm;
+    for (unsigned i = t0; i < cap; i += stride) queue[i] = 0u;
+    for (unsigned g = 0; g < n_nasm; g++) {
+        const NasmDev G = nasms[g];
+        for (unsigned i = t0; i < G.n_tiles; i += stride) G.dep[i] = 0u;
+        if (t0 == 0) { G.svc[SVC_STARTED] = G.svc_base; G.svc[SVC_IDLE] = 1u; G.svc[SVC_COUNT] = 0u; }
+    }
+    if (t0 == 0) {
+        ctrl->head = 0u; ctrl->tail = 0u; ctrl->done = 0u; ctrl->total = total; ctrl->cap = cap;
+        ctrl->abort = 0u; ctrl->stop = 0u; ctrl->stall_ns = stall_ns; ctrl->pipe_ns = pipe_ns;
+        ctrl->svc_stop = svc_stop; ctrl->svc_close = 0u; ctrl->busy = 0u; ctrl->idle_ns = idle_ns;
+    }
+}
+
 // Resets the counters of every graph in the run and seeds the queue with the tiles that only
 // depend on input tiles (push_first_layer_to_rpool, ref src/dse.c:443-470).
 static __global__ void arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, unsigned total, unsigned n_init_total,
@@ -130,7 +225,7 @@ static __global__ void seed_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queu
     }
 }
 
-template <bool TENSOR_CORES, bool ATTENTION>
+template <bool TENSOR_CORES, bool ATTENTION, bool SERVICE>
 __device__ __forceinline__ void run_tile(const LayerDev &L, const TileDev &T, const NasmDev &G, unsigned char *stage_mem, tc::Shared *sh,
                                          tc::PipeState &ps, CtrlDev *ctrl, StatusHost *status) {
     const unsigned tid = threadIdx.x;
@@ -158,6 +253,7 @@ __device__ __forceinline__ void run_tile(const LayerDev &L, const TileDev &T, co
         case SOFTMAX_LAYER: if (tid < tc::NW) tile_softmax(L, T, tid, tc::NW); break;
         case YOLO_LAYER: if (tid < tc::NW) tile_yolo(L, T, tid, tc::NW); break;
         case APPEND_LAYER: if (tid < tc::NW) tile_append(L, T, tid, tc::NW); break;
+        case INPUT_LAYER: if (SERVICE && tid < tc::NW) tile_input(G.input, L, T, tid, tc::NW); break;
         default: break;
     }
 }
@@ -193,6 +289,7 @@ __device__ __forceinline__ bool wait_posted(unsigned long long *bar, unsigned pa
     return false;
 }
 
+template <bool SERVICE>
 static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, CtrlDev *ctrl, unsigned *queue, StatusHost *status,
                                tc::Shared *sh, unsigned long long *my_prof) {
     const unsigned lane = threadIdx.x & 31u;
@@ -208,7 +305,7 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
     unsigned last_done = 0;
     unsigned long long t_progress = __shfl_sync(0xffffffffu, global_ns(), 0), t_mark = t_progress;
     const unsigned long long window = ctrl->stall_ns;
-    unsigned idle_spins = 0, turn = 0, flags = 0, done = 0;
+    unsigned idle_spins = SERVICE ? 30u : 0u, turn = 0, flags = 0, done = 0;   // service: the first idle turns already look for a pass to start
     while (true) {
         bool progressed = false;
         // control state is read by lane 0 and broadcast so the warp never diverges on it
@@ -217,6 +314,7 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
             unsigned f = 0, d = 0;
             if (lane == 0) {
                 f = (ld_relaxed(&ctrl->abort) != 0u ? 1u : 0u) | (ld_relaxed(&ctrl->stop) != 0u ? 2u : 0u);
+                if (SERVICE && ld_relaxed(&ctrl->svc_close) != 0u) f |= 4u;
                 d = ld_relaxed(&ctrl->done);
             }
             flags = __shfl_sync(0xffffffffu, f, 0);
@@ -231,7 +329,7 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
             if (ok) {
                 if (my_prof && lane == 0) t_mark = global_ns();
                 if (!(flags & 1u)) {
-                    unsigned child = complete_children(nasms[fl_nasm[k]], fl_off[k], fl_cnt[k], ctrl, queue, kept == ASPEN_TILE_NONE);
+                    unsigned child = complete_children<SERVICE>(nasms[fl_nasm[k]], fl_off[k], fl_cnt[k], ctrl, queue, kept == ASPEN_TILE_NONE);
                     if (child != ASPEN_TILE_NONE) kept = child;
                     acct_nasm = fl_nasm[k]; acct_layer = fl_layer[k];
                 }
@@ -269,9 +367,10 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
             if (T.flags & TILE_WRITTEN_BY_PARENTS) {
                 // nothing to execute: the tiles it waited for wrote its values; it completes right here
                 if (!(flags & 1u)) {
-                    unsigned child = complete_children(nasms[g], T.child_off, T.child_cnt, ctrl, queue, kept == ASPEN_TILE_NONE);
+                    unsigned child = complete_children<SERVICE>(nasms[g], T.child_off, T.child_cnt, ctrl, queue, kept == ASPEN_TILE_NONE);
                     if (child != ASPEN_TILE_NONE) kept = child;
-                    complete_accounting(nasms[g], T.layer, ctrl, status);
+                    if (SERVICE) svc_account(nasms, n_nasm, g, ctrl, queue);
+                    else complete_accounting(nasms[g], T.layer, ctrl, status);
                 }
             } else {
                 const unsigned k = issued & 1u;
@@ -283,9 +382,13 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
             next = ASPEN_TILE_NONE;
             progressed = true;
         }
-        if (acct_layer != ASPEN_TILE_NONE) { complete_accounting(nasms[acct_nasm], acct_layer, ctrl, status); acct_layer = ASPEN_TILE_NONE; }
+        if (acct_layer != ASPEN_TILE_NONE) {
+            if (SERVICE) svc_account(nasms, n_nasm, acct_nasm, ctrl, queue);
+            else complete_accounting(nasms[acct_nasm], acct_layer, ctrl, status);
+            acct_layer = ASPEN_TILE_NONE;
+        }
         // 4. end of run / stall detection
-        if (done >= total) closed = true;
+        if (!SERVICE && done >= total) closed = true;
         if (issued == retired) {
             if (closed && (next == ASPEN_TILE_NONE || halt)) break;
             if (no_tickets && next == ASPEN_TILE_NONE && kept == ASPEN_TILE_NONE && ticket == ASPEN_TILE_NONE) break;   // can never get work again
@@ -298,7 +401,22 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
         if (((++idle_spins) & 31u) == 0u) {
             unsigned long long now = lane == 0 ? global_ns() : 0ull;
             now = __shfl_sync(0xffffffffu, now, 0);
-            if (now - t_progress > window && issued == retired) {
+            unsigned svc = 1u;
+            if (SERVICE && issued == retired && !closed) {
+                // an idle CTA looks for passes to start, and decides when the kernel has nothing left to wait for
+                svc = svc_scan(nasms, n_nasm, ctrl, queue);
+                if (svc & 4u) t_progress = now;
+                else if (!(svc & 1u)) {
+                    unsigned leave = (svc & 2u) ? 1u : 0u;
+                    if (lane == 0 && !leave) leave = (ld_relaxed(&ctrl->svc_stop) != 0u || now - t_progress > ctrl->idle_ns) ? 1u : 0u;
+                    leave = __shfl_sync(0xffffffffu, leave, 0);
+                    if (leave) {
+                        if (lane == 0) atomicExch(&ctrl->svc_close, 1u);
+                        closed = true;
+                    }
+                }
+            }
+            if (now - t_progress > window && issued == retired && (svc & 1u)) {
                 // nothing running here, nothing completed anywhere for a whole window: the graph cannot progress
                 if (lane == 0 && atomicCAS(&ctrl->abort, 0u, (unsigned)ASPEN_B200_ERR_STALL) == 0u) {
                     status->info0 = ticket; status->info1 = done; status->status = ASPEN_B200_ERR_STALL;
@@ -316,7 +434,8 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
 // ATTENTION: the instantiation that contains the fused attention tile.  It is a kernel of its own because the mere presence
 // of that code changes the register allocation of the contraction tile's main loop (measured: the whole kernel 40 % slower);
 // graphs without a fused attention layer run the instantiation without it.
-template <bool TENSOR_CORES, bool ATTENTION = false>
+// SERVICE: the kernel serves pass after pass of its graphs until the host stops it (see "service mode" above).
+template <bool TENSOR_CORES, bool ATTENTION = false, bool SERVICE = false>
 __global__ void __launch_bounds__(SCHED_THREADS, 1)
 scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHost *status, unsigned long long *prof) {
     extern __shared__ unsigned char smem_raw[];
@@ -351,7 +470,7 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
     unsigned long long *my_prof = prof ? prof + (size_t)blockIdx.x * PROF_SLOTS : nullptr;
 
     if (warp == (SCHED_THREADS >> 5) - 1u) {
-        scheduler_warp(nasms, n_nasm, ctrl, queue, status, sh, my_prof);
+        scheduler_warp<SERVICE>(nasms, n_nasm, ctrl, queue, status, sh, my_prof);
     } else {
         unsigned long long t_mark = my_prof ? global_ns() : 0ull;
         for (unsigned seq = 0;; seq++) {
@@ -363,7 +482,7 @@ scheduler_kernel(const NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, StatusHos
             const NasmDev &G = nasms[sh->tile_nasm[k]];
             const TileDev T = sh->tile_desc[k];
             const LayerDev &L = G.layers[T.layer];
-            run_tile<TENSOR_CORES, ATTENTION>(L, T, G, stage_mem, sh, ps, ctrl, status);
+            run_tile<TENSOR_CORES, ATTENTION, SERVICE>(L, T, G, stage_mem, sh, ps, ctrl, status);
             if (my_prof && tid == 0) {
                 unsigned long long now = global_ns();
                 my_prof[2 + T.layer % PROF_LAYERS] += now - t_mark; my_prof[2 + PROF_LAYERS + T.layer % PROF_LAYERS] += 1ull; t_mark = now;

@@ -376,6 +376,72 @@ __device__ __forceinline__ GemmView gemm_view(const LayerDev &L, const TileDev &
     return g;
 }
 
+// Layer-0 tile (service mode only): the uploaded input becomes the columns of the layer's activation matrix that the
+// tile covers -- what the host-launched unpack / rounding / embedding-gather / padded-copy kernels do for a run that
+// is launched per graph.  Sources are read through L2 (the host's DMA wrote them while this kernel was running).
+static __device__ void tile_input(const InputDev &I, const LayerDev &L, const TileDev &T, unsigned tid, unsigned nthr) {
+    const unsigned H = L.H;
+    if (I.ids) {
+        const unsigned m4 = T.tile_h >> 2;
+        for (unsigned i = tid; i < T.tile_w * m4; i += nthr) {
+            const unsigned c = i / m4, j = T.pos_h + (i - c * m4) * 4u;
+            const size_t t = T.pos_w + c;
+            int id = __ldcg(I.ids + t);
+            id = id < 0 ? 0 : (id >= (int)I.emb_vocab ? (int)I.emb_vocab - 1 : id);
+            float4 v = __ldg(reinterpret_cast<const float4 *>(I.emb_tok + (size_t)id * H + j));
+            if (I.emb_pos) {
+                const float4 p = __ldg(reinterpret_cast<const float4 *>(I.emb_pos + (size_t)(t % I.emb_seq) * H + j));
+                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+            }
+            if (I.round) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
+            *reinterpret_cast<float4 *>(L.out + t * L.ldc + j) = v;
+        }
+        return;
+    }
+    if (I.padded && I.stage && H <= 4u && T.pos_h == 0u) {
+        // an image: one thread per pixel reads its (up to four) channels once and writes both copies
+        for (unsigned c = tid; c < T.tile_w; c += nthr) {
+            const size_t w = T.pos_w + c, hw = (size_t)I.IH * I.IW, b = w / hw, r = w - b * hw;
+            const unsigned ih = (unsigned)(r / I.IW), iw = (unsigned)(r - (size_t)ih * I.IW);
+            const float *src = I.stage + w * H;
+            float *dst = L.out + w * L.ldc;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            v.x = ldcg1(src);
+            if (H > 1u) v.y = ldcg1(src + 1);
+            if (H > 2u) v.z = ldcg1(src + 2);
+            if (H > 3u) v.w = ldcg1(src + 3);
+            if (I.round) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
+            dst[0] = v.x;
+            if (H > 1u) dst[1] = v.y;
+            if (H > 2u) dst[2] = v.z;
+            if (H > 3u) dst[3] = v.w;
+            reinterpret_cast<float4 *>(I.padded)[(b * I.PH + ih + I.pad) * I.PW + iw + I.pad] = v;
+        }
+        return;
+    }
+    if (I.stage || I.round)
+        for (unsigned i = tid; i < T.tile_w * T.tile_h; i += nthr) {
+            const unsigned c = i / T.tile_h, m = T.pos_h + (i - c * T.tile_h);
+            const size_t w = T.pos_w + c;
+            float *dst = L.out + w * L.ldc + m;
+            float v = I.stage ? ldcg1(I.stage + w * H + m) : ldcg1(dst);
+            *dst = I.round ? tf32_round(v) : v;
+        }
+    if (I.padded && T.pos_h == 0u)
+        for (unsigned c = tid; c < T.tile_w; c += nthr) {
+            const size_t w = T.pos_w + c, hw = (size_t)I.IH * I.IW, b = w / hw, r = w - b * hw;
+            const unsigned ih = (unsigned)(r / I.IW), iw = (unsigned)(r - (size_t)ih * I.IW);
+            const float *src = I.stage ? I.stage + w * H : L.out + w * L.ldc;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            v.x = ldcg1(src);
+            if (I.IC > 1) v.y = ldcg1(src + 1);
+            if (I.IC > 2) v.z = ldcg1(src + 2);
+            if (I.IC > 3) v.w = ldcg1(src + 3);
+            if (I.round) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
+            reinterpret_cast<float4 *>(I.padded)[(b * I.PH + ih + I.pad) * I.PW + iw + I.pad] = v;
+        }
+}
+
 static __device__ void tile_gemm_ffma(const LayerDev L, const TileDev T, unsigned tid, unsigned nthr) {
     const GemmView g = gemm_view(L, T);
     const unsigned mg = (T.tile_h + 3) >> 2;             // groups of 4 output rows

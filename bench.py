@@ -268,8 +268,8 @@ class Net:
         return int(self.ids.nbytes if self.ids is not None else self.x.nbytes)
 
     def add_graph(self):
-        """A second tile graph of the same network in the same rpool (for the double-buffered end-to-end loop and the
-        co-inference figure).  Not before the device-timed blocks: a timed launch drains every graph of the pool."""
+        """One more tile graph of the same network in the same rpool (the graphs in rotation of the service-mode legs).  Not
+        before the per-launch timed blocks: a timed launch drains every graph of the pool."""
         q_h, q_w, mn = self.tiling
         self.L.aspen_b200_set_tile_quanta(q_h, q_w, 100000000)
         n_ = self.api.Nasm(self.dnn, self.batch, self.seq, mn)
@@ -291,6 +291,49 @@ class Net:
             ms.append(t)
         return ms, launches
 
+    def serve(self, graphs: int = 3):
+        """Service mode (aspen_b200_dse_group_set_service) with `graphs` tile graphs of the network in rotation, each run once."""
+        while len(self.nasms) < graphs:
+            self.add_graph()
+        self.group.set_service(True)
+        for n_ in self.nasms:
+            self.feed(n_)
+        self.group.run()
+        for n_ in self.nasms:
+            self.group.wait(n_)
+        self.group.stop()
+
+    def time_served(self, warmup: int, steps: int, blocks: int):
+        """`blocks` device-timed regions (CUDA events on the engine's stream) of exactly `steps` passes, dealt round robin to
+        the graphs in rotation, inside one resident scheduler launch per region; every pass starts with the input layer's
+        tiles (scatter / rounding of the resident input)."""
+        ms, launches = [], 0
+        for b in range(blocks):
+            t, launches = self.group.time_passes(warmup if b == 0 else 2, steps)
+            ms.append(t)
+        return ms, launches
+
+    def e2e_served(self, steps: int) -> float:
+        """The serving loop in service mode: dse_group_run once, then per step rpool_add_nasm_raw_input (host -> device copy of
+        the step's input, next to the graphs being computed), dse_wait_for_nasm_completion and dse_get_nasm_result (device ->
+        host) of the oldest request; two requests are in the kernel while the third uploads."""
+        g, n = self.nasms, len(self.nasms)
+        t0 = time.perf_counter()
+        self.feed(g[0]); self.group.run()
+        if steps > 1:
+            self.feed(g[1 % n])
+        out = None
+        for k in range(steps):
+            if k + 2 < steps:
+                self.feed(g[(k + 2) % n])
+            self.group.wait(g[k % n])
+            out = g[k % n].result(self.order)
+        self.group.stop()
+        ms = (time.perf_counter() - t0) * 1e3     # exactly `steps` uploads, completed passes and downloads
+        assert self.group.status() == 0 and np.isfinite(out).all()
+        self.out = out
+        return ms
+
     def e2e_serial(self, steps: int) -> float:
         nasm = self.nasms[0]
         t0 = time.perf_counter()
@@ -301,29 +344,6 @@ class Net:
             self.group.stop()
             self.out = nasm.result(self.order)  # dse_get_nasm_result: device -> host read of the step's result
         return (time.perf_counter() - t0) * 1e3
-
-    def e2e_overlapped(self, steps: int) -> float:
-        """Same calls, two graphs of the network in flight (the serving loop of a user who double-buffers): while the
-        scheduler kernel works on one graph, the next step's input uploads and the previous step's result downloads on
-        the library's transfer stream.  Every timed iteration still contains one host -> device input copy, one
-        completed graph and one device -> host result read."""
-        pair, cur = self.nasms[:2], 0
-        t0 = time.perf_counter()
-        self.feed(pair[cur]); self.group.run()      # step 1 starts inside the timed region
-        out = None
-        for _ in range(steps - 1):
-            nxt = cur ^ 1
-            self.feed(pair[nxt])                # upload of the next step's input, under the current graph's kernel
-            self.group.wait(pair[cur])
-            self.group.stop()
-            self.group.run()                    # next graph starts
-            out = pair[cur].result(self.order)  # result of the finished graph, under the next graph's kernel
-            cur = nxt
-        self.group.wait(pair[cur]); self.group.stop(); out2 = pair[cur].result(self.order)
-        ms = (time.perf_counter() - t0) * 1e3   # exactly `steps` uploads, runs and downloads
-        assert np.isfinite(out2).all() and (out is None or np.array_equal(out, out2))
-        self.out = out2
-        return ms
 
     def close(self):
         if self.own_group:
@@ -427,41 +447,42 @@ def main():
     net.warm()
     sampler.wait_first(5.0)
 
-    # ---- device-timed runs (inputs resident in HBM): `blocks` regions of exactly `steps` passes ----
+    # ---- one scheduler launch per step, one graph (inputs scattered beforehand): the explanatory figure ----
     barrier(world, True)
-    block_ms, launches = net.time_blocks(args.warmup, args.steps, args.blocks)
+    pl_ms, _ = net.time_blocks(args.warmup, args.steps, 3)
+    pl_max = float(np.median([reduce_max(t, world, True) for t in pl_ms]))
+    barrier(world, True)
+    net.e2e_serial(2)
+    barrier(world, True)
+    serial_max = reduce_max(net.e2e_serial(args.steps), world, True)
+    single_out = net.out.copy()
+
+    # ---- the headline: service mode, device-timed (inputs resident in HBM): `blocks` regions of exactly `steps` passes ----
+    net.serve(3)
+    barrier(world, True)
+    block_ms, launches = net.time_served(args.warmup, args.steps, args.blocks)
     clocks = sampler.stop()
     block_max = [reduce_max(t, world, True) for t in block_ms]
     barrier(world, True)
     ms, max_ms = float(np.median(block_ms)), float(np.median(block_max))
 
-    # ---- end to end through the public API: host input -> H2D -> run -> D2H result ----
-    net.e2e_serial(2)
+    # ---- end to end through the public API: host input -> H2D -> pass -> D2H result, every step ----
+    net.e2e_served(4)
     barrier(world, True)
-    serial_max = reduce_max(net.e2e_serial(args.steps), world, True)
-    barrier(world, True)
-    net.add_graph()
-    net.e2e_overlapped(3)
-    barrier(world, True)
-    e2e_max = reduce_max(net.e2e_overlapped(args.steps), world, True)
+    e2e_max = reduce_max(net.e2e_served(args.steps), world, True)
     barrier(world, True)
     out = net.out
-
-    # Extra, not the headline: both graphs armed in ONE scheduler launch (the reference's co-inference: several
-    # nasms in one rpool).  Twice the ready tiles per layer for the same 148 SMs.
-    for n_ in net.nasms:
-        net.feed(n_)
-    co_iters = max(args.steps // 2, 1)
-    co_ms, _ = net.group.time_runs(2, co_iters)
-    co_value = 2 * batch * co_iters * world / (reduce_max(co_ms, world, True) * 1e-3)
-    barrier(world, True)
+    assert np.array_equal(out, single_out), "a served pass must give the values of a launched run"
+    net.group.set_service(False)
+    per_launch = {"value": job_value(batch, args.steps, world, pl_max), "unit": "inf/s", "ms_per_step": pl_max / args.steps,
+                  "note": "one graph, dse_group_run launches the scheduler once per step, input scattered before the timed region"}
 
     extras = {}
     if not args.no_extras:
         extras = extra_legs(args, rank, world, wd, net, workload)
 
     if rank == 0:
-        report(args, world, workload, batch, net, ms, max_ms, block_max, e2e_max, serial_max, launches, clocks, out, wd, co_value, extras)
+        report(args, world, workload, batch, net, ms, max_ms, block_max, e2e_max, serial_max, launches, clocks, out, wd, per_launch, extras)
     net.close()
     if world > 1:
         import torch.distributed as dist
@@ -502,13 +523,17 @@ def extra_legs(args, rank, world, wd, net, workload):
         b = Net("bert_base", WORKLOADS["bert_base"][1], wd, tokens=30522)
         b.warm()
         barrier(world, True)
-        bms, _ = b.time_blocks(3, steps, 3)
+        pms, _ = b.time_blocks(3, steps, 3)
+        pmax = float(np.median([reduce_max(t, world, True) for t in pms]))
+        b.serve(3)
+        barrier(world, True)
+        bms, _ = b.time_served(3, steps, 3)
         bmax = float(np.median([reduce_max(t, world, True) for t in bms]))
-        b.add_graph()
-        b.e2e_overlapped(3)
+        b.e2e_served(4)
         barrier(world, True)
-        be2e = reduce_max(b.e2e_overlapped(steps), world, True)
+        be2e = reduce_max(b.e2e_served(steps), world, True)
         barrier(world, True)
+        b.group.set_service(False)
         tf = b.flops * steps / (float(np.median(bms)) * 1e-3) / 1e12
         extras["bert_base"] = {"metric": "sequences_per_sec", "config": {"workload": "bert_base_s128_bs32_per_gpu", "tile_quanta": list(b.tiling[:2]),
                                                                           "min_ninst_per_ldata": b.tiling[2], "tiles": b.nasms[0].num_ninst},
@@ -516,6 +541,7 @@ def extra_legs(args, rank, world, wd, net, workload):
                                "e2e": {"value": job_value(b.batch, steps, world, be2e), "unit": "seq/s", "h2d_bytes_per_step": b.h2d_bytes,
                                        "input": "token ids (int32), embedded on the device",
                                        "d2h_bytes_per_step": int(b.out.nbytes)},
+                               "per_launch": {"value": job_value(b.batch, steps, world, pmax), "unit": "seq/s", "ms_per_step": pmax / steps},
                                "achieved_tflops": tf, "flops_per_step": b.flops}
         b.close()
     # ---- strong scaling (configs[1]): the global batch of 32 split 32 / N per GPU, results gathered on rank 0 ----
@@ -563,7 +589,7 @@ def extra_legs(args, rank, world, wd, net, workload):
     return extras
 
 
-def report(args, world, workload, batch, net, ms, max_ms, block_max, e2e_max, serial_max, launches, clocks, out, wd, co_value, extras):
+def report(args, world, workload, batch, net, ms, max_ms, block_max, e2e_max, serial_max, launches, clocks, out, wd, per_launch, extras):
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -581,19 +607,22 @@ def report(args, world, workload, batch, net, ms, max_ms, block_max, e2e_max, se
         "data": "synthetic",
         "config": {"workload": f"{workload}_bs{batch}_per_gpu", "seq_len": seq or None, "tile_profile": "b200 tensor-core quanta",
                    "tile_quanta": list(net.tiling[:2]), "min_ninst_per_ldata": net.tiling[2], "tiles": nasm.num_ninst, "flops_per_step": flops,
+                   "execution": f"service mode: {len(net.nasms)} tile graphs of batch {batch} in rotation inside one resident scheduler launch per "
+                                "timed block; every step is one complete pass of one graph, input layer's scatter included",
                    "l2": f"no flush: each step streams a {net.arena_bytes / 1e9:.2f} GB activation arena (> 126 MB L2)"},
         "timing": {"blocks": len(block_max), "block_ms": [round(t, 4) for t in block_max], "reported": "median block", "spread_frac": spread},
         "clocks": clocks,
         "e2e": {"value": job_value(batch, args.steps, world, e2e_max), "unit": "inf/s", "h2d_bytes_per_step": net.h2d_bytes,
                 "d2h_bytes_per_step": int(out.nbytes), "ms_per_step": e2e_max / args.steps,
-                "mode": "two graphs in flight: input upload and result download overlap the other graph's kernel",
+                "mode": "service mode: per step one rpool_add_nasm_raw_input (upload), one completed pass, one dse_get_nasm_result (download); "
+                        "two requests in the resident kernel while the third uploads",
                 "serial_value": job_value(batch, args.steps, world, serial_max), "serial_ms_per_step": serial_max / args.steps},
         "gpu_launches": launches,
-        "co_inference": {"graphs_per_launch": 2, "value": co_value, "unit": "inf/s",
-                         "note": "two batch-sized graphs of the network in one rpool and one scheduler launch, inputs resident"},
+        "per_launch": per_launch,
         "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
                      "traffic": TRAFFIC_BYTES.get(workload), "peak_source": peak_src,
-                     "note": "kernel = persistent scheduler_kernel<true> (whole tile graph, all layer types); operands are TF32: see peak_tf32"},
+                     "note": "kernel = persistent scheduler_kernel<true, false, true> (whole tile graphs, all layer types; one launch per timed block); "
+                             "operands are TF32: see peak_tf32"},
     }
     if world == 1 and not args.no_extras:
         try:

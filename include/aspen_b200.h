@@ -204,6 +204,27 @@ long aspen_b200_nasm_get_ldata_packed(nasm_t *nasm, unsigned int ldata_idx, floa
  * the number of kernel launches issued.  Returns a negative value on error. */
 double aspen_b200_group_time_runs(dse_group_t *dse_group, unsigned int warmup, unsigned int iters, unsigned long long *launches_out);
 
+/* Service mode of a dse group.  The reference's DSE threads live from dse_group_run to dse_group_stop and serve
+ * whatever rpool_add_nasm brings in the meantime (ref src/dse.c:20-108, 215-232; src/rpool.c:390-685).  With the mode
+ * on, this library does the same on the device: dse_group_run launches ONE scheduler kernel over the graphs of the
+ * pool and that kernel stays resident; rpool_add_nasm / rpool_add_nasm_raw_input / aspen_b200_rpool_add_nasm_tokens /
+ * rpool_reset_nasm on a graph it serves upload the input and ask for one more pass of the graph (a graph takes one
+ * request at a time: a second request first waits for the pass that is owed); dse_wait_for_nasm_completion waits for
+ * the pass last asked for; dse_get_nasm_result and the layer readers copy with the copy engine; dse_group_stop ends
+ * the kernel once nothing is running or owed.  Passes of different graphs overlap on the SMs, so the late, narrow
+ * layers of one request run next to the early, wide layers of the next.  The input layer's tiles run on the device
+ * (scatter, TF32 rounding, embedding gather), so nothing but copies is issued while the kernel is resident; calls
+ * that must allocate or free device memory (a graph's first use, its destruction) stop the kernel first and the next
+ * run or wait starts it again.  Left idle for 20 ms (ASPEN_B200_IDLE_MS) the kernel leaves by itself.
+ * Off by default: each dse_group_run then launches the scheduler for the graphs armed at that moment.
+ * Returns 0, or -1 on error.  Graphs that use the fused attention tile are not served in this mode. */
+int aspen_b200_dse_group_set_service(dse_group_t *dse_group, int on);
+
+/* Timed execution in service mode: `passes` passes dealt round robin to the graphs of the group's rpool (inputs as
+ * they are on the device), inside service launches that end when the passes are complete; returns the device time in
+ * milliseconds between CUDA events on the group's stream, a negative value on error. */
+double aspen_b200_group_time_passes(dse_group_t *dse_group, unsigned int warmup, unsigned int passes, unsigned long long *launches_out);
+
 /* Time accounting of the device scheduler (replaces the reference's wall-clock probes,
  * ref src/util.c:490-539).  Active when the environment variable ASPEN_B200_PROFILE is set before
  * dse_group_init.  out[516], summed over all worker CTAs since the last call: [0] scheduler polls
