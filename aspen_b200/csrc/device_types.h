@@ -122,6 +122,7 @@ struct CtrlDev {
     unsigned svc_stop;       // host request: leave once no pass is running or asked for
     unsigned svc_close;      // set by the device: everybody leaves (no error)
     unsigned busy;           // graphs with a pass in progress
+    unsigned svc_ahead;      // a busy CTA lines up a second tile when at least this many ready tiles wait unclaimed (0: never)
     unsigned long long idle_ns;    // leave after this long without a pass in progress
 };
 

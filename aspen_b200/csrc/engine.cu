@@ -205,6 +205,7 @@ struct Engine {
     std::vector<nasm_t *> svc_pool;   // every graph of the group's rpool that has a device image: what the next launch serves
     unsigned long long idle_ns = 20000000ull;   // the kernel leaves after this long with no pass running
     cudaEvent_t svc_armed_ev = nullptr;
+    unsigned svc_ahead = 32, run_ahead = 0;   // see CtrlDev::svc_ahead: in service mode / in a launch per run
     float *xfer = nullptr;            // device staging for packed inputs / results
     unsigned long long *prof = nullptr;   // per-CTA time accounting, allocated when ASPEN_B200_PROFILE is set
     size_t xfer_bytes = 0;
@@ -316,6 +317,8 @@ Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) 
                 : cudaFuncSetAttribute(sched::scheduler_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->smem_bytes)) == cudaSuccess;
         ok = ok && cudaEventCreateWithFlags(&e->svc_armed_ev, cudaEventDisableTiming) == cudaSuccess;
         if (env_u64("ASPEN_B200_IDLE_MS", &v) && v > 0) e->idle_ns = v * 1000000ull;
+        if (env_u64("ASPEN_B200_SVC_AHEAD", &v)) e->svc_ahead = (unsigned)v;
+        if (env_u64("ASPEN_B200_RUN_AHEAD", &v)) e->run_ahead = (unsigned)v;
     }
     if (ok && getenv("ASPEN_B200_PROFILE")) {
         size_t bytes = (size_t)e->n_ctas * sched::PROF_SLOTS * sizeof(unsigned long long);
@@ -1082,7 +1085,7 @@ static int launch_run(Engine *e, const std::vector<nasm_t *> &run) {
     e->status_h->status = 0;
     e->status_h->tiles_done = 0;
     unsigned arm_blocks = std::min<unsigned>((total + 255) / 256, 1024);
-    sched::arm_kernel<<<arm_blocks, 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue, total, n_init, n_input, e->stall_ns, e->pipe_ns);
+    sched::arm_kernel<<<arm_blocks, 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue, total, n_init, n_input, e->stall_ns, e->pipe_ns, e->run_ahead);
     sched::seed_kernel<<<std::max(1u, std::min<unsigned>((n_init + 255) / 256, 256)), 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue);
     bool any_attention = false;
     for (nasm_t *nasm : run) any_attention |= nasm->dev->fused_attention;
@@ -1324,7 +1327,7 @@ static int svc_launch(Engine *e, const std::vector<nasm_t *> &graphs, unsigned s
     e->status_h->status = 0;
     e->status_h->tiles_done = 0;
     sched::svc_arm_kernel<<<std::min<unsigned>((cap + 255) / 256, 2048), 256, 0, e->stream>>>(e->nasms_d, e->ctrl, e->queue, cap, total, e->stall_ns, e->pipe_ns,
-                                                                                               e->idle_ns, stop_when_done);
+                                                                                               e->idle_ns, stop_when_done, e->svc_ahead);
     if (e->precision == 0)
         sched::scheduler_kernel<true, false, true><<<e->n_ctas, sched::SCHED_THREADS, e->smem_bytes, e->stream>>>(e->nasms_d, e->ctrl, e->queue, e->status_d, e->prof);
     else

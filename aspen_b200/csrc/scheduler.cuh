@@ -181,7 +181,7 @@ static __device__ void svc_account(const NasmDev *nasms, unsigned n_nasm, unsign
 
 // Arms a service launch: empty queue, zero counters, every graph idle at the pass count the host has seen complete.
 static __global__ void svc_arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, unsigned cap, unsigned total, unsigned long long stall_ns,
-                               unsigned long long pipe_ns, unsigned long long idle_ns, unsigned svc_stop) {
+                               unsigned long long pipe_ns, unsigned long long idle_ns, unsigned svc_stop, unsigned svc_ahead) {
     const unsigned stride = gridDim.x * blockDim.x, t0 = blockIdx.x * blockDim.x + threadIdx.x;
     const unsigned n_nasm = ctrl->n_nasm;
     for (unsigned i = t0; i < cap; i += stride) queue[i] = 0u;
@@ -193,14 +193,14 @@ static __global__ void svc_arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *q
     if (t0 == 0) {
         ctrl->head = 0u; ctrl->tail = 0u; ctrl->done = 0u; ctrl->total = total; ctrl->cap = cap;
         ctrl->abort = 0u; ctrl->stop = 0u; ctrl->stall_ns = stall_ns; ctrl->pipe_ns = pipe_ns;
-        ctrl->svc_stop = svc_stop; ctrl->svc_close = 0u; ctrl->busy = 0u; ctrl->idle_ns = idle_ns;
+        ctrl->svc_stop = svc_stop; ctrl->svc_close = 0u; ctrl->busy = 0u; ctrl->idle_ns = idle_ns; ctrl->svc_ahead = svc_ahead;
     }
 }
 
 // Resets the counters of every graph in the run and seeds the queue with the tiles that only
 // depend on input tiles (push_first_layer_to_rpool, ref src/dse.c:443-470).
 static __global__ void arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue, unsigned total, unsigned n_init_total,
-                           unsigned n_input_total, unsigned long long stall_ns, unsigned long long pipe_ns) {
+                           unsigned n_input_total, unsigned long long stall_ns, unsigned long long pipe_ns, unsigned ahead) {
     const unsigned stride = gridDim.x * blockDim.x, t0 = blockIdx.x * blockDim.x + threadIdx.x;
     const unsigned n_nasm = ctrl->n_nasm;
     for (unsigned i = t0; i < total; i += stride) queue[i] = 0u;
@@ -213,7 +213,7 @@ static __global__ void arm_kernel(NasmDev *nasms, CtrlDev *ctrl, unsigned *queue
     }
     if (t0 == 0) {
         ctrl->head = 0u; ctrl->tail = n_init_total; ctrl->done = n_input_total; ctrl->total = total; ctrl->cap = total;
-        ctrl->abort = 0u; ctrl->stop = 0u; ctrl->stall_ns = stall_ns; ctrl->pipe_ns = pipe_ns;
+        ctrl->abort = 0u; ctrl->stop = 0u; ctrl->stall_ns = stall_ns; ctrl->pipe_ns = pipe_ns; ctrl->svc_ahead = ahead;
     }
 }
 // Second step of arming (after every slot was cleared): write the initial ready tiles.
@@ -305,7 +305,8 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
     unsigned last_done = 0;
     unsigned long long t_progress = __shfl_sync(0xffffffffu, global_ns(), 0), t_mark = t_progress;
     const unsigned long long window = ctrl->stall_ns;
-    unsigned idle_spins = SERVICE ? 30u : 0u, turn = 0, flags = 0, done = 0;   // service: the first idle turns already look for a pass to start
+    unsigned idle_spins = SERVICE ? 30u : 0u, turn = 0, flags = 0, done = 0, ahead_turn = 0;
+    const unsigned ahead = ctrl->svc_ahead;   // service: the first idle turns already look for a pass to start
     while (true) {
         bool progressed = false;
         // control state is read by lane 0 and broadcast so the warp never diverges on it
@@ -346,7 +347,16 @@ static __device__ void scheduler_warp(const NasmDev *nasms, unsigned n_nasm, Ctr
                 // Only an idle CTA queues up for the next ready tile.  Claiming one while still busy was
                 // measured to cost 40 % of throughput: the claimed tile waits in this CTA's mailbox while
                 // other SMs that could have started it at once sit idle.
-                const bool take = ticket == ASPEN_TILE_NONE && !no_tickets && issued == retired;
+                bool take = ticket == ASPEN_TILE_NONE && !no_tickets && issued == retired;
+                if (ahead != 0u && !take && ticket == ASPEN_TILE_NONE && !no_tickets && issued - retired == 1u && (ahead_turn++ & 15u) == 0u) {
+                    // Busy with one tile, nothing lined up.  With several requests in the kernel the queue usually holds ready
+                    // tiles that no idle CTA is waiting for: taking one now lets the executors go from this tile straight to
+                    // the next while the completion (child counters, queue pushes) runs beside them.  Only with a backlog: a
+                    // ticket held for a tile that is not there yet would keep that tile from an idle SM.
+                    int backlog = 0;
+                    if (lane == 0) backlog = (int)(ld_relaxed(&ctrl->tail) - ld_relaxed(&ctrl->head));
+                    take = __shfl_sync(0xffffffffu, backlog, 0) >= (int)ahead;
+                }
                 if (take) {
                     unsigned t = lane == 0 ? atomicAdd(&ctrl->head, 1u) : 0u;
                     ticket = __shfl_sync(0xffffffffu, t, 0);
