@@ -211,14 +211,27 @@ class Nasm:
         nbytes = lib().dse_get_nasm_result(self.h, arr, C.byref(ptr))
         if nbytes < 0:
             raise RuntimeError("dse_get_nasm_result failed: " + last_error())
-        out = np.frombuffer(C.string_at(ptr, nbytes), dtype=np.float32).copy()
-        lib()._free(ptr)
-        return out
+        return np.asarray(_OwnedBuffer(ptr, nbytes))      # the library's buffer itself, no copy
 
     def close(self):
         if self.h:
             lib().apu_destroy_nasm(self.h)
             self.h = None
+
+
+class _OwnedBuffer:
+    """A malloc'ed float buffer handed over by the library: numpy arrays made from it (and their views) keep this object
+    as their base, and the buffer is freed with it."""
+
+    def __init__(self, ptr: C.c_void_p, nbytes: int):
+        self._ptr = ptr
+        self.__array_interface__ = {"data": (ptr.value, False), "shape": (nbytes // 4,), "typestr": "<f4", "version": 3}
+
+    def __del__(self):
+        try:
+            lib()._free(self._ptr)
+        except Exception:  # noqa: BLE001 -- interpreter shutdown: the process's memory goes away with it
+            pass
 
 
 class Rpool:
