@@ -75,6 +75,9 @@ def main():
     ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"])
     ap.add_argument("--profile", default="b200", choices=["reference", "b200"])
     ap.add_argument("--quanta", type=int, nargs=2, metavar=("H", "W"), help="tile row / column quanta (overrides --profile)")
+    ap.add_argument("--service", type=int, default=0, metavar="GRAPHS",
+                    help="service mode: this many graphs of the network in rotation inside one resident scheduler launch")
+    ap.add_argument("--drop-pre-add", action="store_true", help="aspen_b200_set_hidden_states(0): outputs that only a fused residual add reads are not written")
     ap.add_argument("--layer-table", action="store_true", help="per-layer-class time accounting (see the module docstring)")
     ap.add_argument("--tensor-peak", type=float, default=1353.0, help="TFLOP/s the per-SM tensor fractions are quoted against")
     ap.add_argument("--hbm-peak", type=float, default=6454.9, help="GB/s the per-SM bandwidth fractions are quoted against")
@@ -93,8 +96,11 @@ def main():
         L.aspen_b200_set_tile_quanta(args.quanta[0], args.quanta[1], 100000000)
     else:
         L.aspen_b200_set_tile_profile(1 if args.profile == "b200" else 0)
+    if args.drop_pre_add:
+        L.aspen_b200_set_hidden_states(0)
     dnn = api.Dnn(cfg, wfile)
     nasm = api.Nasm(dnn, args.batch, args.seq, args.min_ninst)
+    others = [api.Nasm(dnn, args.batch, args.seq, args.min_ninst) for _ in range(max(args.service - 1, 0))]
     L.aspen_b200_set_tile_profile(0)
     rpool = api.Rpool()
     group = api.DseGroup(0, 0 if args.precision == "tf32" else 1)
@@ -102,10 +108,24 @@ def main():
     i0 = nasm.ldata_info(0)
     x = np.random.default_rng(0).standard_normal((i0["W"], i0["H"]), dtype=np.float32)
     rpool.add(nasm, x)
-    if args.layer_table:
-        group.time_runs(1, 1)
-        group.profile()                                   # clears the counters of the first-touch run
-    ms, launches = group.time_runs(args.warmup, args.iters)
+    if args.service:
+        # every graph once (images built, first touch), then the timed passes dealt round robin inside resident launches
+        group.set_service(True)
+        for n_ in others:
+            rpool.add(n_, x)
+        group.run()
+        for n_ in [nasm] + others:
+            group.wait(n_)
+        group.stop()
+        if args.layer_table:
+            group.profile()
+        timed = group.time_passes
+    else:
+        if args.layer_table:
+            group.time_runs(1, 1)
+            group.profile()                               # clears the counters of the first-touch run
+        timed = group.time_runs
+    ms, launches = timed(args.warmup, args.iters)
     flops = nasm.total_flops
     print(f"{args.net} batch {args.batch} seq {args.seq}: {nasm.num_ninst} tiles, {ms / args.iters:.3f} ms/run, "
           f"{flops * args.iters / ms / 1e9:.1f} TFLOP/s, {launches} launches, status {group.status()}")
@@ -120,7 +140,10 @@ def main():
             print(f"per CTA and run (us): tiles {busy / n / 1e3:.1f}, waiting for a ready tile {p['wait_ns'] / n / 1e3:.1f}, "
                   f"completion + child updates (scheduler warp) {p['complete_ns'] / n / 1e3:.1f}; {p['ctas']} CTAs")
             print(layer_table(api, nasm, dnn, p, runs, p["ctas"], args.tensor_peak, args.hbm_peak))
-    group.close(); nasm.close(); rpool.close(); dnn.close()
+    group.close()
+    for n_ in others:
+        n_.close()
+    nasm.close(); rpool.close(); dnn.close()
 
 
 if __name__ == "__main__":
