@@ -41,8 +41,9 @@ WORKLOADS = {
     "bert_base": ("bert_base", 32, 128, "n002", 3, 3),
     "vgg16": ("vgg16", 16, 0, "he", 2, 2),
 }
-# DRAM bytes per scheduler launch, from the ncu capture summarised in profiles/ (batch-4 case scaled by 8).
-TRAFFIC_BYTES = {"resnet50": 2.99e9}
+# DRAM bytes per pass, from the ncu capture of the service-mode kernel summarised in profiles/ (265 MB per batch-4 pass, scaled by 8:
+# activation traffic grows with the batch).  A timed launch serves `steps` passes.
+TRAFFIC_BYTES_PER_STEP = {"resnet50": 2.12e9}
 # Tiling of the nasm per workload: (row quantum, column quantum, min_ninst_per_ldata).  Tensor-core shaped
 # quanta; the values a graph computes do not depend on them.  Each is the best of a measured sweep
 # (quanta 64-256, min_ninst 100-592).
@@ -631,7 +632,8 @@ def report(args, world, workload, batch, net, ms, max_ms, block_max, e2e_max, se
         "gpu_launches": launches,
         "per_launch": per_launch,
         "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved_tf / peak_tf,
-                     "traffic": TRAFFIC_BYTES.get(workload), "peak_source": peak_src,
+                     "traffic": TRAFFIC_BYTES_PER_STEP[workload] * args.steps if workload in TRAFFIC_BYTES_PER_STEP else None,
+                     "traffic_per_step": TRAFFIC_BYTES_PER_STEP.get(workload), "peak_source": peak_src,
                      "note": "kernel = persistent scheduler_kernel<true, false, true> (whole tile graphs, all layer types; one launch per timed block); "
                              "operands are TF32: see peak_tf32"},
     }
