@@ -400,11 +400,11 @@ static __device__ void tile_input(const InputDev &I, const LayerDev &L, const Ti
     }
     if (I.padded && I.stage && H <= 4u && T.pos_h == 0u) {
         // an image: one thread per pixel reads its (up to four) channels once and writes both copies
+        const unsigned hw = I.IH * I.IW;
         for (unsigned c = tid; c < T.tile_w; c += nthr) {
-            const size_t w = T.pos_w + c, hw = (size_t)I.IH * I.IW, b = w / hw, r = w - b * hw;
-            const unsigned ih = (unsigned)(r / I.IW), iw = (unsigned)(r - (size_t)ih * I.IW);
-            const float *src = I.stage + w * H;
-            float *dst = L.out + w * L.ldc;
+            const unsigned w = T.pos_w + c, b = w / hw, r = w - b * hw, ih = r / I.IW, iw = r - ih * I.IW;
+            const float *src = I.stage + (size_t)w * H;
+            float *dst = L.out + (size_t)w * L.ldc;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             v.x = ldcg1(src);
             if (H > 1u) v.y = ldcg1(src + 1);
@@ -415,11 +415,22 @@ static __device__ void tile_input(const InputDev &I, const LayerDev &L, const Ti
             if (H > 1u) dst[1] = v.y;
             if (H > 2u) dst[2] = v.z;
             if (H > 3u) dst[3] = v.w;
-            reinterpret_cast<float4 *>(I.padded)[(b * I.PH + ih + I.pad) * I.PW + iw + I.pad] = v;
+            reinterpret_cast<float4 *>(I.padded)[((size_t)b * I.PH + ih + I.pad) * I.PW + iw + I.pad] = v;
         }
         return;
     }
-    if (I.stage || I.round)
+    if ((I.stage || I.round) && ((T.tile_h | T.pos_h | L.ldc | H) & 3u) == 0u) {
+        // 16-byte pieces: consecutive threads take consecutive pieces of a column
+        const unsigned m4 = T.tile_h >> 2;
+        for (unsigned i = tid; i < T.tile_w * m4; i += nthr) {
+            const unsigned c = i / m4, m = T.pos_h + (i - c * m4) * 4u;
+            const size_t w = T.pos_w + c;
+            float *dst = L.out + w * L.ldc + m;
+            float4 v = I.stage ? ldcg4(I.stage + w * H + m) : ldcg4(dst);
+            if (I.round) { v.x = tf32_round(v.x); v.y = tf32_round(v.y); v.z = tf32_round(v.z); v.w = tf32_round(v.w); }
+            *reinterpret_cast<float4 *>(dst) = v;
+        }
+    } else if (I.stage || I.round)
         for (unsigned i = tid; i < T.tile_w * T.tile_h; i += nthr) {
             const unsigned c = i / T.tile_h, m = T.pos_h + (i - c * T.tile_h);
             const size_t w = T.pos_w + c;
