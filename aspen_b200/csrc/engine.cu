@@ -318,6 +318,7 @@ Engine *engine_create(int device, int precision, unsigned int /*num_dse_hint*/) 
         ok = ok && cudaEventCreateWithFlags(&e->svc_armed_ev, cudaEventDisableTiming) == cudaSuccess;
         if (env_u64("ASPEN_B200_IDLE_MS", &v) && v > 0) e->idle_ns = v * 1000000ull;
         if (env_u64("ASPEN_B200_SVC_AHEAD", &v)) e->svc_ahead = (unsigned)v;
+        if (env_u64("ASPEN_B200_SERVICE", &v)) e->service = v != 0;      // for programs that cannot call aspen_b200_dse_group_set_service
         if (env_u64("ASPEN_B200_RUN_AHEAD", &v)) e->run_ahead = (unsigned)v;
     }
     if (ok && getenv("ASPEN_B200_PROFILE")) {
