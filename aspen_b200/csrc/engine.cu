@@ -713,10 +713,10 @@ static int build_device_nasm(Engine *e, nasm_t *nasm) {
     // OFF unless ASPEN_B200_ATTN_FUSE=1: the fused tile itself takes 13 us where the two tiles it replaces take 20
     // (BERT-base, 128 x 128 x 64 per head), but the kernel instantiation that contains it runs every other tile type about
     // 1.5 x slower (its register allocation spills on the common path, and with 176 KB of shared memory per CTA little L1
-    // is left to absorb spills), a net loss for now.
+    // is left to absorb spills), a net loss for now.  Not for a group in service mode (that kernel has no fused tile).
     std::vector<unsigned char> attn_bypassed(nasm->num_ldata, 0);
     const char *want_attn = getenv("ASPEN_B200_ATTN_FUSE");
-    if (e->precision == 0 && want_attn && atoi(want_attn) != 0) {
+    if (e->precision == 0 && !e->service && want_attn && atoi(want_attn) != 0) {
         for (unsigned i = 1; i < nasm->num_ldata; i++) {
             if (nasm->ldata[i].layer->type != V_ATTENTION_LAYER) continue;
             LayerDev &V = layers[i];
