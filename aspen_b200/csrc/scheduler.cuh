@@ -12,8 +12,9 @@
 // There is no kernel boundary and no barrier between layers: a tile fires as soon as its own
 // parent tiles are complete.
 //
-// The queue is a ticket ring: every tile is pushed at most once per run, so a ring of `total`
-// slots never wraps; slot value = global tile id + 1, 0 = not yet filled.  A popper that holds a
+// The queue is a ticket ring: every tile is pushed at most once per run (per pass in service mode,
+// where the ring holds a fixed number of passes and the kernel is launched again when they are used
+// up), so it never wraps; slot value = global tile id + 1, 0 = not yet filled.  A popper that holds a
 // ticket whose slot is still empty waits -- bounded: when no tile anywhere completes for
 // `stall_ns` it records ASPEN_B200_ERR_STALL, raises the abort flag and every CTA leaves.
 //
