@@ -1454,7 +1454,7 @@ int engine_set_service(Engine *e, int on) {
     if (!e) return -1;
     CUDA_TRY(cudaSetDevice(e->device));
     if (e->service == (on != 0)) return 0;
-    if (e->service) { if (svc_halt(e) != 0) return -1; }
+    if (e->service) { if (svc_halt(e) != 0) return -1; e->svc_pool.clear(); }
     else if (e->running) { cudaStreamSynchronize(e->stream); e->running = false; e->in_flight.clear(); }
     e->service = on != 0;
     return 0;
