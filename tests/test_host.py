@@ -323,3 +323,30 @@ def test_batchnorm_is_folded_on_load_like_the_reference(workdir):
         assert len(want) == len(got)
         for a, b in zip(got, want):
             np.testing.assert_allclose(a, b, rtol=2e-6, atol=1e-9)   # the reference is built with -Ofast: not bit-exact
+
+
+def test_result_arrays_own_the_library_buffer():
+    """Nasm.result hands back the malloc'ed buffer of dse_get_nasm_result without copying it: the array and every view
+    of it keep the buffer alive, and it is freed exactly once when the last of them goes."""
+    import ctypes as C
+    import gc
+    libc = C.CDLL(None)
+    libc.malloc.restype = C.c_void_p
+    libc.malloc.argtypes = [C.c_size_t]
+    freed = []
+    real_free = api.lib()._free
+    api.lib()._free = lambda p: (freed.append(p.value), real_free(p))
+    try:
+        ptr = C.c_void_p(libc.malloc(64))
+        C.memset(ptr, 0, 64)
+        arr = np.asarray(api._OwnedBuffer(ptr, 64))
+        arr[:] = np.arange(16, dtype=np.float32)
+        view = arr.reshape(4, 4)[1:]
+        del arr
+        gc.collect()
+        assert not freed and view.sum() == sum(range(4, 16))
+        del view
+        gc.collect()
+        assert freed == [ptr.value]
+    finally:
+        api.lib()._free = real_free
