@@ -588,7 +588,8 @@ def extra_legs(args, rank, world, wd, net, workload):
         name, nb = assign
         m = Net(name, nb, wd, graphs=1)
         m.warm()
-        m.serve(4)
+        m_rotation = max(4, min(12, 96 // nb))      # as for the strong split: the smaller the shard, the more of them in rotation
+        m.serve(m_rotation)
         barrier(world, True)
         mms, _ = m.time_served(3, steps, 3)
         mmax = float(np.median([reduce_max(t, world, True) for t in mms]))
@@ -596,7 +597,7 @@ def extra_legs(args, rank, world, wd, net, workload):
         m.group.set_service(False)
         mine = gather_objects((name, nb, float(np.median(mms)) / steps), world)
         extras["by_model"] = {"config": {"workload": "resnet50_bs16_plus_vgg16_bs16", "assignment": [[p[0], p[1]] for p in mine],
-                                         "execution": "service mode, 4 graphs in rotation per GPU"},
+                                         "execution": f"service mode, {m_rotation} graphs in rotation per GPU"},
                               "value": 32 * steps / (mmax * 1e-3), "unit": "inf/s", "ms_per_step": mmax / steps,
                               "ms_per_step_per_rank": [p[2] for p in mine]}
         m.close()
