@@ -436,7 +436,8 @@ def main():
             print(json.dumps({"metric": "inferences_per_sec", "value": job_value(batch, args.steps, world, max_ms), "unit": "inf/s",
                               "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": max_ms / args.steps,
                               "scaling": "weak", "data": "dry-run", "higher_is_better": True,
-                              "strong": {"shards": [p[1] for p in parts]}, "by_model": {"assignment": [p[2] for p in parts]}}), flush=True)
+                              "strong": {"shards": [p[1] for p in parts], "graphs_in_rotation": graphs_in_rotation(batch // world)},
+                              "by_model": {"assignment": [p[2] for p in parts]}}), flush=True)
         return
 
     from aspen_b200 import api
@@ -497,6 +498,13 @@ def main():
         dist.destroy_process_group()
 
 
+def graphs_in_rotation(samples: int) -> int:
+    """Graphs a GPU keeps in rotation in service mode for shards of `samples` samples.  A small shard leaves most SMs idle in its
+    narrow layers, so more of them are kept in flight (measured on one GPU: 12 graphs of 4 samples run at 0.39 ms per pass,
+    8 at 0.43, 4 at 0.65; batch-32 graphs gain nothing beyond 4)."""
+    return max(4, min(12, 96 // max(samples, 1)))
+
+
 def strong_shard(global_batch: int, rank: int, world: int):
     """Samples [lo, hi) of the global batch that rank `rank` of `world` computes (configs[1]: 32 -> 32 / N per GPU)."""
     per = global_batch // world
@@ -555,9 +563,8 @@ def extra_legs(args, rank, world, wd, net, workload):
     gb = WORKLOADS[workload][1]
     if world > 1 and gb % world == 0:
         lo, hi = strong_shard(gb, rank, world)
-        # every GPU serves its samples of one global batch after the other; a small shard leaves most SMs idle in its narrow
-        # layers, so more shards are kept in rotation (measured: 12 graphs of 4 samples run at 0.39 ms per pass, 4 graphs at 0.65)
-        rotation = max(4, min(12, 96 // (hi - lo)))
+        # every GPU serves its samples of one global batch after the other
+        rotation = graphs_in_rotation(hi - lo)
         s = Net(workload, hi - lo, wd, graphs=1)
         rows = net.x.shape[0] // gb
         s.x_pinned.copy_(net.x_pinned[lo * rows:hi * rows])       # this rank's samples of the global batch
@@ -588,7 +595,7 @@ def extra_legs(args, rank, world, wd, net, workload):
         name, nb = assign
         m = Net(name, nb, wd, graphs=1)
         m.warm()
-        m_rotation = max(4, min(12, 96 // nb))      # as for the strong split: the smaller the shard, the more of them in rotation
+        m_rotation = graphs_in_rotation(nb)
         m.serve(m_rotation)
         barrier(world, True)
         mms, _ = m.time_served(3, steps, 3)

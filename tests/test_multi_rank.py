@@ -24,6 +24,7 @@ def test_two_rank_launch_aggregates_the_slowest_rank():
     # the two splits of the multi-GPU legs: global batch 32 cut in rank order; one network per half of the ranks
     assert rec["strong"]["shards"] == [[0, 16], [16, 32]]
     assert rec["by_model"]["assignment"] == [["resnet50", 16], ["vgg16", 16]]
+    assert rec["strong"]["graphs_in_rotation"] == 6
 
 
 def test_splits_for_eight_ranks():
@@ -32,6 +33,8 @@ def test_splits_for_eight_ranks():
     assert [bench.strong_shard(32, r, 8) for r in range(8)] == [[4 * r, 4 * r + 4] for r in range(8)]
     assert [bench.by_model_assignment(r, 8) for r in range(8)] == [["resnet50", 4]] * 4 + [["vgg16", 4]] * 4
     assert bench.by_model_assignment(0, 1) is None
+    # service mode keeps more shards in rotation the smaller they are
+    assert [bench.graphs_in_rotation(n) for n in (32, 16, 8, 4, 1)] == [4, 6, 12, 12, 12]
 
 
 def test_reference_arm_runs_on_rank_zero_only():
