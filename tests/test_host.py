@@ -195,6 +195,10 @@ def test_error_conventions(workdir, capfd):
     L.rpool_add_nasm_raw_input(rp, None, None)
     assert "nasm is NULL" in api.last_error()
     L.rpool_destroy(rp)
+    # service mode and its timer need a dse group
+    assert L.aspen_b200_dse_group_set_service(None, 1) == -1
+    assert "dse_group is NULL" in api.last_error()
+    assert L.aspen_b200_group_time_passes(None, 1, 1, None) < 0
     nasm.close()
     dnn.close()
     capfd.readouterr()
